@@ -1,0 +1,41 @@
+"""NVLink topology check run at Buffer construction.
+
+The reference only checks devices whose name contains 'PCIE': at most two ranks, and NVML must report
+an NVLink P2P path for each pair (deep_ep/utils.py:64-101). The same rule is applied here; on SXM/HGX
+parts (B200) every pair is connected through NVSwitch and nothing needs checking.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+def check_nvlink_connections(group: Optional["dist.ProcessGroup"], nvml=None) -> None:
+    """Assert that PCIe-form-factor GPUs of the group are NVLink-bridged. ``nvml`` lets tests inject a fake
+    ``pynvml`` module."""
+    if group is None or not torch.cuda.is_available():
+        return
+    name = torch.cuda.get_device_name(torch.cuda.current_device())
+    if "PCIE" not in name.upper():
+        return
+    assert group.size() <= 2, "PCIe GPUs only have pairwise NVLink connections"
+    if nvml is None:
+        import pynvml as nvml  # provided by nvidia-ml-py
+    nvml.nvmlInit()
+    try:
+        devices = os.environ.get("CUDA_VISIBLE_DEVICES", "0,1,2,3,4,5,6,7").strip(",").split(",")
+        physical = int(devices[torch.cuda.current_device()])
+        ids = [None] * group.size()
+        dist.all_gather_object(ids, physical, group)
+        handles = [nvml.nvmlDeviceGetHandleByIndex(i) for i in ids]
+        for i, a in enumerate(handles):
+            for j, b in enumerate(handles):
+                if i >= j:
+                    continue
+                status = nvml.nvmlDeviceGetP2PStatus(a, b, nvml.NVML_P2P_CAPS_INDEX_NVLINK)
+                assert status == nvml.NVML_P2P_STATUS_OK, f"GPU {ids[i]} and GPU {ids[j]} are not connected via NVLink"
+    finally:
+        nvml.nvmlShutdown()

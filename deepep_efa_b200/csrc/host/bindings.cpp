@@ -16,8 +16,24 @@
 #include "../kernels/gemm_api.h"
 #include "runtime.hpp"
 
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
 namespace py = pybind11;
 using dxh::RuntimeCore;
+
+// Debug aid (DEEPEP_DEBUG_SEGV=1): print the native call stack of a crashing thread before the default
+// action runs, so that a host-side fault in this extension can be located without a debugger.
+static void dx_segv_handler(int sig) {
+    void* frames[64];
+    const int n = backtrace(frames, 64);
+    const char msg[] = "\n[deepep_efa_b200] fatal signal, native backtrace:\n";
+    (void)!write(2, msg, sizeof(msg) - 1);
+    backtrace_symbols_fd(frames, n, 2);
+    signal(sig, SIG_DFL);
+    raise(sig);
+}
 
 namespace {
 
@@ -535,6 +551,10 @@ void bind_gemm(py::module_& m);  // gemm_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "deepep_efa_b200 native runtime (sm_100a)";
+    if (const char* e = std::getenv("DEEPEP_DEBUG_SEGV"); e != nullptr && e[0] == '1') {
+        signal(SIGSEGV, dx_segv_handler);
+        signal(SIGBUS, dx_segv_handler);
+    }
 
     py::class_<dxh::Config>(m, "Config")
         .def(py::init<int, int, int, int, int>(), py::arg("num_sms") = 32, py::arg("num_max_nvl_chunked_send_tokens") = 6,

@@ -1,9 +1,130 @@
 // Python bindings of the grouped expert GEMM (kept in its own translation unit so that kernel-side
 // changes do not rebuild the runtime bindings).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+
+#include <map>
+#include <mutex>
 
 #include "../kernels/gemm_api.h"
 
 namespace py = pybind11;
 
-void bind_gemm(py::module_& m) { (void)m; }
+namespace {
+
+#define DXG_CHECK(cond, msg)                                                                  \
+    do {                                                                                      \
+        if (!(cond)) throw std::invalid_argument(std::string("deepep_efa_b200.grouped_gemm: ") + (msg)); \
+    } while (0)
+
+// One error word per device: set by a kernel whose bounded pipeline wait ran out.
+torch::Tensor error_flag(int device) {
+    static std::mutex mu;
+    static std::map<int, torch::Tensor> flags;
+    std::lock_guard<std::mutex> g(mu);
+    auto it = flags.find(device);
+    if (it == flags.end()) {
+        auto t = torch::zeros({1}, torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, device));
+        it = flags.emplace(device, t).first;
+    }
+    return it->second;
+}
+
+int sm_count(int device) {
+    static std::map<int, int> cache;
+    auto it = cache.find(device);
+    if (it != cache.end()) return it->second;
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+    cache[device] = n;
+    return n;
+}
+
+// mode 0: a [M,K], b [G,N,K] (or [G*N,K]), m_offsets [G+1] -> c [M, N] (or [M, N/2] with swiglu)
+// mode 1: a [N_out, M], b [K_out, M], m_offsets [G+1] -> c [G, N_out, K_out]
+torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& m_offsets, int mode, bool swiglu,
+                           c10::optional<torch::Tensor> a_scales, c10::optional<torch::Tensor> b_scales,
+                           c10::optional<torch::Tensor> out, int num_sms, double timeout_ms) {
+    DXG_CHECK(a.is_cuda() && b.is_cuda() && m_offsets.is_cuda(), "operands must be CUDA tensors");
+    DXG_CHECK(a.is_contiguous() && b.is_contiguous() && m_offsets.is_contiguous(), "operands must be contiguous");
+    DXG_CHECK(m_offsets.scalar_type() == torch::kInt32 && m_offsets.dim() == 1 && m_offsets.numel() >= 2, "m_offsets must be int32 [G+1]");
+    const bool fp8 = a.scalar_type() == torch::kFloat8_e4m3fn;
+    DXG_CHECK(fp8 || a.scalar_type() == torch::kBFloat16, "A must be bf16 or float8_e4m3fn");
+    DXG_CHECK(b.scalar_type() == a.scalar_type(), "A and B must have the same dtype");
+    DXG_CHECK(a.dim() == 2, "A must be 2-D");
+    DXG_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "operands must be 16-byte aligned");
+    const int G = (int)m_offsets.numel() - 1;
+    const int device = a.device().index();
+    c10::cuda::CUDAGuard guard(device);
+    dx::GroupedGemmArgs p{};
+    p.num_groups = G;
+    p.mode = mode;
+    p.fp8 = fp8 ? 1 : 0;
+    p.swiglu = swiglu ? 1 : 0;
+    torch::Tensor c;
+    auto bf16 = a.options().dtype(torch::kBFloat16);
+    if (mode == 0) {
+        const int64_t M = a.size(0), K = a.size(1);
+        DXG_CHECK(b.numel() % ((int64_t)G * K) == 0, "B must be [G, N, K]");
+        const int64_t N = b.numel() / ((int64_t)G * K);
+        DXG_CHECK(b.size(-1) == K, "B's last dimension must equal K");
+        DXG_CHECK(!swiglu || N % 2 == 0, "swiglu needs an even N (gate and up stacked)");
+        const int64_t out_cols = swiglu ? N / 2 : N;
+        c = out.has_value() ? *out : torch::empty({M, out_cols}, bf16);
+        DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && c.numel() == M * out_cols, "out must be contiguous bf16 [M, N]");
+        p.m_total = (int)M;
+        p.n = (int)N;
+        p.k = (int)K;
+        if (fp8) {
+            DXG_CHECK(a_scales.has_value() && b_scales.has_value(), "fp8 operands need a_scales and b_scales");
+            DXG_CHECK(a_scales->scalar_type() == torch::kFloat32 && a_scales->is_contiguous() && a_scales->numel() == M * (K / 128), "a_scales must be f32 [M, K/128]");
+            DXG_CHECK(b_scales->scalar_type() == torch::kFloat32 && b_scales->is_contiguous() && b_scales->numel() == (int64_t)G * (N / 128) * (K / 128), "b_scales must be f32 [G, N/128, K/128]");
+            p.a_scales = a_scales->data_ptr<float>();
+            p.b_scales = b_scales->data_ptr<float>();
+        }
+    } else {
+        DXG_CHECK(mode == 1 && !fp8 && !swiglu, "K-grouped mode is bf16 only, without swiglu");
+        DXG_CHECK(b.dim() == 2 && a.size(1) == b.size(1), "mode 1: A [N_out, M] and B [K_out, M] must share M");
+        const int64_t n_out = a.size(0), k_out = b.size(0), M = a.size(1);
+        c = out.has_value() ? *out : torch::empty({(int64_t)G, n_out, k_out}, bf16);
+        DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && c.numel() == (int64_t)G * n_out * k_out, "out must be contiguous bf16 [G, N_out, K_out]");
+        p.m_total = (int)M;
+        p.n = (int)n_out;
+        p.k = (int)k_out;
+    }
+    p.a = a.data_ptr();
+    p.b = b.data_ptr();
+    p.c = c.data_ptr();
+    p.m_offsets = m_offsets.data_ptr<int>();
+    p.num_sms = num_sms > 0 ? num_sms : sm_count(device);
+    p.error_flag = error_flag(device).data_ptr<int>();
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device);
+    p.timeout_cycles = (long long)(timeout_ms * (double)(khz > 0 ? khz : 1965000));
+    const cudaError_t e = dx::launch_grouped_gemm(p, at::cuda::getCurrentCUDAStream(device).stream());
+    if (e == cudaErrorInvalidValue) {
+        cudaGetLastError();
+        throw std::invalid_argument(
+            "deepep_efa_b200.grouped_gemm: unsupported shape (need K % 64 == 0 for bf16 / % 128 for fp8, N % 128 == 0, group "
+            "boundaries on multiples of 128)");
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        throw std::runtime_error(std::string("deepep_efa_b200.grouped_gemm: launch failed: ") + cudaGetErrorString(e));
+    }
+    return c;
+}
+
+int gemm_error(int device) { return error_flag(device).item<int>(); }
+void gemm_clear_error(int device) { error_flag(device).zero_(); }
+
+}  // namespace
+
+void bind_gemm(py::module_& m) {
+    m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
+          py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
+          py::arg("timeout_ms") = 2000.0);
+    m.def("gemm_error", &gemm_error);
+    m.def("gemm_clear_error", &gemm_clear_error);
+}

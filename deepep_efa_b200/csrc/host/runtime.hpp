@@ -13,11 +13,11 @@
 
 #include <atomic>
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <deque>
 #include <memory>
 #include <mutex>
-#include <sstream>
 #include <stdexcept>
 #include <string>
 #include <thread>
@@ -29,15 +29,16 @@
 
 namespace dxh {
 
-#define DX_CUDA_CHECK(expr)                                                                                   \
-    do {                                                                                                      \
-        cudaError_t _e = (expr);                                                                              \
-        if (_e != cudaSuccess) {                                                                              \
-            std::ostringstream _s;                                                                            \
-            _s << "CUDA error " << cudaGetErrorName(_e) << " (" << cudaGetErrorString(_e) << ") at " << __FILE__ \
-               << ":" << __LINE__ << ": " #expr;                                                              \
-            throw std::runtime_error(_s.str());                                                               \
-        }                                                                                                     \
+#define DX_CUDA_CHECK(expr)                                                                              \
+    do {                                                                                                 \
+        cudaError_t _e = (expr);                                                                         \
+        if (_e != cudaSuccess) {                                                                         \
+            char _buf[512];                                                                              \
+            std::snprintf(_buf, sizeof(_buf), "CUDA error %s (%s) at %s:%d: %s", cudaGetErrorName(_e),   \
+                          cudaGetErrorString(_e), __FILE__, __LINE__, #expr);                            \
+            cudaGetLastError();                                                                          \
+            throw std::runtime_error(_buf);                                                              \
+        }                                                                                                \
     } while (0)
 
 inline const char* status_name(int code) {
@@ -182,12 +183,14 @@ class RuntimeCore {
             off = arena_.alloc(bytes);
         }
         if (off < 0) {
-            std::ostringstream s;
-            s << "symmetric arena exhausted: need " << bytes << " B, capacity " << arena_.capacity() << " B, in use "
-              << arena_.in_use() << " B, largest free block " << arena_.largest_free()
-              << " B. Create the Buffer with a larger num_nvl_bytes (Config.get_nvl_buffer_size_hint) or drop "
-                 "references to earlier dispatch results.";
-            throw std::runtime_error(s.str());
+            char buf[512];
+            std::snprintf(buf, sizeof(buf),
+                          "symmetric arena exhausted: need %llu B, capacity %llu B, in use %llu B, largest free block %llu B. "
+                          "Create the Buffer with a larger num_nvl_bytes (Config.get_nvl_buffer_size_hint) or drop references "
+                          "to earlier dispatch results.",
+                          (unsigned long long)bytes, (unsigned long long)arena_.capacity(), (unsigned long long)arena_.in_use(),
+                          (unsigned long long)arena_.largest_free());
+            throw std::runtime_error(buf);
         }
         return (uint64_t)off;
     }
@@ -251,12 +254,13 @@ class RuntimeCore {
         }
     }
 
-    int status_code() const { return host_->status.code; }
+    int status_code() const { return read_word(&host_->status.code); }
     std::string status_string() const {
-        const dx::StatusBlock s = const_cast<const dx::StatusBlock&>(host_->status);
-        std::ostringstream o;
-        o << status_name(s.code) << " [code " << s.code << ", rank " << s.rank << ", peer " << s.peer << ", detail " << s.detail << "]";
-        return o.str();
+        const int code = read_word(&host_->status.code), rank = read_word(&host_->status.rank);
+        const int peer = read_word(&host_->status.peer), detail = read_word(&host_->status.detail);
+        char buf[256];
+        std::snprintf(buf, sizeof(buf), "%s [code %d, rank %d, peer %d, detail %d]", status_name(code), code, rank, peer, detail);
+        return std::string(buf);
     }
     void clear_status() { std::memset((void*)&host_->status, 0, sizeof(dx::StatusBlock)); }
     void raise_status(const char* where) {
@@ -289,6 +293,8 @@ class RuntimeCore {
     dx::ControlBlock* control() const { return reinterpret_cast<dx::ControlBlock*>(base_); }
 
   private:
+    static int read_word(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
+
     struct Pending {
         uint64_t off;
         std::vector<cudaEvent_t> events;

@@ -1,8 +1,45 @@
-// Launch API of the grouped expert GEMM kernels (tcgen05 / TMEM / TMA, sm_100a). No torch headers.
+// Launch API of the grouped expert GEMM (tcgen05 / TMEM / TMA, sm_100a). No torch headers.
+//
+//   C[m, n] = sum_k A[m, k] * B[n, k]        (both operands K-major, fp32 accumulation in TMEM)
+//
+// mode 0, "M-grouped" (expert forward and input gradients): A is [M_total, K]; rows
+//   [m_offsets[g], m_offsets[g+1]) belong to expert g and use weight block B[g*N : (g+1)*N, :].
+//   Group boundaries must be multiples of 128 (dispatch's expert alignment / the permute pads).
+// mode 1, "K-grouped" (weight gradients): A is [N_out, M_total], B is [K_out, M_total]; expert g
+//   reduces over columns [m_offsets[g], m_offsets[g+1]) and writes C[g*N_out : (g+1)*N_out, :].
+//
+// Operand types: BF16 (kind::f16) or FP8 e4m3 with DeepSeek-style scales (one fp32 per 1x128 of A and
+// per 128x128 of B): every 128-deep K block is accumulated in its own TMEM window and promoted into
+// fp32 registers with the product of the two scales.
+// swiglu = 1: B holds [gate; up] stacked per expert ([G, 2*I, K]); a tile computes matching gate and up
+//   columns and writes silu(gate) * up, so C is [M_total, I].
 #pragma once
 
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace dx {
+
+struct GroupedGemmArgs {
+    const void* a;            // operand A (see mode)
+    const void* b;            // operand B
+    void* c;                  // bf16 output
+    const float* a_scales;    // fp8 only: [M_total, K/128]
+    const float* b_scales;    // fp8 only: [G, N/128, K/128]
+    const int* m_offsets;     // [G+1] device memory
+    int num_groups;
+    int mode;                 // 0 = M-grouped, 1 = K-grouped
+    int fp8;                  // 0 = bf16 operands, 1 = e4m3 operands (mode 0 only)
+    int swiglu;               // mode 0 only
+    int m_total;              // rows of A (mode 0) / reduction length (mode 1)
+    int n;                    // mode 0: rows of B per expert (2*I when swiglu); mode 1: N_out (rows of A)
+    int k;                    // mode 0: reduction length; mode 1: K_out (rows of B)
+    int num_sms;              // persistent grid size
+    int* error_flag;          // device int, set non-zero when a bounded pipeline wait ran out
+    long long timeout_cycles;
+};
+
+// Returns cudaErrorInvalidValue for unsupported shapes (divisibility rules are in grouped_gemm.cu).
+cudaError_t launch_grouped_gemm(const GroupedGemmArgs& args, cudaStream_t stream);
+
 }  // namespace dx

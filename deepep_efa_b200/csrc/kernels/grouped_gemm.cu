@@ -1,0 +1,571 @@
+// Grouped expert GEMM for sm_100a: tcgen05.mma with the accumulator in TMEM, operands staged into
+// 128-byte-swizzled shared memory by TMA (from this GPU's own memory only, never multicast), a
+// persistent warp-specialised CTA per SM.
+//
+//   warp 0   : TMA producer   (one lane)  global -> smem ring, mbarrier complete_tx
+//   warp 1   : MMA issuer     (one lane)  tcgen05.mma, tcgen05.commit frees smem stages and publishes
+//                                         accumulator windows; also owns TMEM alloc / dealloc
+//   warps 2-5: epilogue       (128 thr)   tcgen05.ld -> registers -> (scale | SwiGLU) -> BF16 -> global
+//
+// A tile is 128 rows x kBlockN columns; a K block is 128 bytes per row (64 BF16 or 128 e4m3), i.e. one
+// swizzle atom, consumed by four MMAs. Two accumulator windows in TMEM let the epilogue of window i
+// overlap the MMAs of window i+1. BF16: a window is a whole output tile. FP8 with DeepSeek-style fp32
+// scales (1x128 on activations, 128x128 on weights): a window is ONE K block; the epilogue multiplies it
+// by scale_a[row, kb] * scale_b[nblock, kb] and accumulates in fp32 registers (the MMA's native block
+// scaling wants power-of-two UE8M0 factors, which these scales are not).
+//
+// Every mbarrier wait is bounded; when a limit runs out the CTA raises a flag, all roles leave their
+// loops, TMEM is released and the kernel returns.
+//
+// The reference has no GEMM: its users run their expert FFN between dispatch and combine themselves.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "gemm_api.h"
+
+namespace dx {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kKBlockBytes = 128;      // one 128B swizzle atom per row
+constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueThreads = 128;
+constexpr int kATileBytes = kBlockM * kKBlockBytes;  // 16 KiB
+constexpr int kMaxGroups = 1024;
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and raises the CTA abort flag) when the limit runs out or another role
+// has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > limit) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+template <bool kFp8>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (kFp8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in 128B-swizzled shared memory: rows are 128 bytes apart, 8-row groups 1024 bytes
+// apart (stride byte offset), descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+    d |= (uint64_t)1 << 46;                        // descriptor version
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp32 accumulate, A and B K-major, M = 128, N = n.
+template <bool kFp8>
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+    uint32_t d = 0;
+    d |= 1u << 4;                          // D format = F32
+    d |= (kFp8 ? 0u : 1u) << 7;            // A format: E4M3 (f8f6f4) or BF16 (f16)
+    d |= (kFp8 ? 0u : 1u) << 10;           // B format
+    d |= (uint32_t)(n >> 3) << 17;         // N / 8
+    d |= (uint32_t)(kBlockM >> 4) << 24;   // M / 16
+    return d;
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+struct TileInfo {
+    int a_row, a_k0, b_row, b_row2, b_k0, num_kb, c_row, c_col, group, nblock, nblock2;
+};
+
+template <int kBlockN, bool kFp8, bool kSwiGLU>
+struct Cfg {
+    static constexpr int kBTileBytes = kBlockN * kKBlockBytes;
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr int kStages = (kBlockN == 256) ? 4 : 6;
+    static constexpr int kTmemCols = 2 * kBlockN;   // two accumulator windows
+    static constexpr int kOutCols = kSwiGLU ? kBlockN / 2 : kBlockN;
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
+};
+
+template <int kBlockN, bool kFp8, bool kSwiGLU>
+__global__ void __launch_bounds__(kNumThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
+    using C = Cfg<kBlockN, kFp8, kSwiGLU>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::kStages * C::kStageBytes);
+    uint64_t* full = bars;                       // [kStages]
+    uint64_t* empty = bars + C::kStages;         // [kStages]
+    uint64_t* tmem_full = bars + 2 * C::kStages; // [2]
+    uint64_t* tmem_empty = tmem_full + 2;        // [2]
+    int* tile_start = reinterpret_cast<int*>(bars + 32);  // [G+1] first tile index of every group
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.num_groups;
+    const int elem_per_kb = kFp8 ? 128 : 64;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        // tile table
+        int run = 0;
+        const int tiles_n = p.mode == 0 ? p.n / kBlockN : 0;
+        const int tiles_fixed = p.mode == 1 ? (p.n / kBlockM) * (p.k / kBlockN) : 0;
+        for (int g = 0; g < G; ++g) {
+            tile_start[g] = run;
+            if (p.mode == 0) {
+                const int rows = p.m_offsets[g + 1] - p.m_offsets[g];
+                run += ((rows + kBlockM - 1) / kBlockM) * tiles_n;
+            } else {
+                run += tiles_fixed;
+            }
+        }
+        tile_start[G] = run;
+    }
+    if (warp == 1) tmem_alloc(&s_tmem_base, C::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    const int total_tiles = tile_start[G];
+    volatile int* abort_flag = &s_abort;
+    const long long limit = p.timeout_cycles;
+
+    // Decodes tile index -> coordinates; `g` is a cursor that only moves forward.
+    auto decode = [&](int tile, int& g, TileInfo& ti) {
+        while (tile >= tile_start[g + 1]) ++g;
+        const int local = tile - tile_start[g];
+        const int m0 = p.m_offsets[g], m1 = p.m_offsets[g + 1];
+        ti.group = g;
+        if (p.mode == 0) {
+            const int tiles_m = (m1 - m0 + kBlockM - 1) / kBlockM;
+            const int nt = local / tiles_m, mt = local % tiles_m;  // consecutive tiles share the weight tile
+            ti.a_row = m0 + mt * kBlockM;
+            ti.a_k0 = 0;
+            ti.b_k0 = 0;
+            ti.num_kb = p.k / elem_per_kb;
+            ti.c_row = ti.a_row;
+            if (kSwiGLU) {
+                const int half = kBlockN / 2, inter = p.n / 2;
+                ti.b_row = g * p.n + nt * half;            // gate rows
+                ti.b_row2 = g * p.n + inter + nt * half;   // up rows
+                ti.c_col = nt * half;
+                ti.nblock = (nt * half) / 128;
+                ti.nblock2 = (inter + nt * half) / 128;
+            } else {
+                ti.b_row = g * p.n + nt * kBlockN;
+                ti.b_row2 = 0;
+                ti.c_col = nt * kBlockN;
+                ti.nblock = (nt * kBlockN) / 128;
+                ti.nblock2 = ti.nblock;
+            }
+        } else {
+            const int tiles_j = p.k / kBlockN;
+            const int it = local / tiles_j, jt = local % tiles_j;
+            ti.a_row = it * kBlockM;
+            ti.b_row = jt * kBlockN;
+            ti.b_row2 = 0;
+            ti.a_k0 = m0;
+            ti.b_k0 = m0;
+            ti.num_kb = (m1 - m0) / elem_per_kb;
+            ti.c_row = g * p.n + it * kBlockM;
+            ti.c_col = jt * kBlockN;
+            ti.nblock = ti.nblock2 = 0;
+        }
+    };
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            int stage = 0, phase = 0, g = 0;
+            TileInfo ti;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                decode(tile, g, ti);
+                for (int kb = 0; kb < ti.num_kb; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, limit)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = stage_base + (size_t)stage * C::kStageBytes;
+                    uint8_t* sb = sa + kATileBytes;
+                    mbar_expect_tx(&full[stage], C::kStageBytes);
+                    tma_load_2d(&map_a, &full[stage], sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
+                    if (kSwiGLU) {
+                        tma_load_2d(&map_b, &full[stage], sb, ti.b_k0 + kb * elem_per_kb, ti.b_row);
+                        tma_load_2d(&map_b, &full[stage], sb + C::kBTileBytes / 2, ti.b_k0 + kb * elem_per_kb, ti.b_row2);
+                    } else {
+                        tma_load_2d(&map_b, &full[stage], sb, ti.b_k0 + kb * elem_per_kb, ti.b_row);
+                    }
+                    if (++stage == C::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            // Own copies in flight land in this CTA's shared memory: wait for them before the CTA may exit.
+            if (!ok) {
+                for (int s = 0; s < C::kStages; ++s) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && clock64() - t0 < limit) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc<kFp8>(kBlockN);
+            int stage = 0, phase = 0, g = 0;
+            int win = 0, win_phase = 0;  // accumulator window ring
+            TileInfo ti;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                decode(tile, g, ti);
+                if (ti.num_kb == 0) continue;  // epilogue writes zeros on its own
+                for (int kb = 0; kb < ti.num_kb; ++kb) {
+                    const bool new_window = kFp8 ? true : (kb == 0);
+                    if (new_window) {
+                        if (!mbar_wait(&tmem_empty[win], win_phase ^ 1, abort_flag, limit)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                    }
+                    if (!mbar_wait(&full[stage], phase, abort_flag, limit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(stage_base + (size_t)stage * C::kStageBytes);
+                    const uint32_t sb = sa + kATileBytes;
+                    const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(win * kBlockN);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // +32 bytes along K inside the swizzle atom = +2 in the 16-byte start-address field
+                        umma<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                   (new_window && j == 0) ? 0u : 1u);
+                    }
+                    umma_commit(&empty[stage]);  // smem stage reusable once these MMAs have read it
+                    const bool window_done = kFp8 ? true : (kb == ti.num_kb - 1);
+                    if (window_done) {
+                        umma_commit(&tmem_full[win]);
+                        if (++win == 2) {
+                            win = 0;
+                            win_phase ^= 1;
+                        }
+                    }
+                    if (++stage == C::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else {
+        // ================= epilogue =================
+        const int q = warp & 3;                    // TMEM lane quarter this warp may read
+        const int row_in_tile = q * 32 + lane;
+        int g = 0, win = 0, win_phase = 0;
+        TileInfo ti;
+        bool ok = true;
+        __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.c);
+        const int ldc = p.mode == 0 ? (kSwiGLU ? p.n / 2 : p.n) : p.k;
+        const int c_rows = p.mode == 0 ? p.m_total : p.num_groups * p.n;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            decode(tile, g, ti);
+            const int row = ti.c_row + row_in_tile;
+            __nv_bfloat16* crow = cbase + (size_t)row * ldc + ti.c_col;
+            if (ti.num_kb == 0) {
+                if (row < c_rows)
+                    for (int c = 0; c < C::kOutCols; c += 8) *reinterpret_cast<int4*>(crow + c) = make_int4(0, 0, 0, 0);
+                continue;
+            }
+            if constexpr (kFp8) {
+                // one window per K block, promoted into fp32 registers with the two scales
+                float acc[kBlockN];
+#pragma unroll
+                for (int i = 0; i < kBlockN; ++i) acc[i] = 0.f;
+                const int num_kscales = p.k / 128;
+                const int n_blocks = p.n / 128;
+                const float* sa_row = p.a_scales + (size_t)min(row, p.m_total - 1) * num_kscales;
+                const float* sb0 = p.b_scales + ((size_t)ti.group * n_blocks + ti.nblock) * num_kscales;
+                const float* sb1 = p.b_scales + ((size_t)ti.group * n_blocks + ti.nblock2) * num_kscales;
+                for (int kb = 0; kb < ti.num_kb; ++kb) {
+                    const float sa = __ldg(sa_row + kb);
+                    const float s0 = sa * __ldg(sb0 + kb), s1 = sa * __ldg(sb1 + kb);
+                    if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
+#pragma unroll
+                    for (int c = 0; c < kBlockN; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + c, v);
+                        tmem_ld_wait();
+                        const float s = (kSwiGLU && c >= kBlockN / 2) ? s1 : s0;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), s, acc[c + i]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[win]);
+                    if (++win == 2) {
+                        win = 0;
+                        win_phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                if (row < c_rows) {
+#pragma unroll
+                    for (int c = 0; c < C::kOutCols; c += 8) {
+                        float o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = kSwiGLU ? silu(acc[c + i]) * acc[kBlockN / 2 + c + i] : acc[c + i];
+                        int4 w;
+                        __nv_bfloat162 t0 = __floats2bfloat162_rn(o[0], o[1]), t1 = __floats2bfloat162_rn(o[2], o[3]);
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(o[4], o[5]), t3 = __floats2bfloat162_rn(o[6], o[7]);
+                        w.x = *reinterpret_cast<int*>(&t0);
+                        w.y = *reinterpret_cast<int*>(&t1);
+                        w.z = *reinterpret_cast<int*>(&t2);
+                        w.w = *reinterpret_cast<int*>(&t3);
+                        *reinterpret_cast<int4*>(crow + c) = w;
+                    }
+                }
+            } else {
+                if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
+#pragma unroll 1
+                for (int c = 0; c < C::kOutCols; c += 32) {
+                    uint32_t v[32];
+                    float o[32];
+                    tmem_ld32(taddr + c, v);
+                    if constexpr (kSwiGLU) {
+                        uint32_t u[32];
+                        tmem_ld32(taddr + kBlockN / 2 + c, u);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = silu(__uint_as_float(v[i])) * __uint_as_float(u[i]);
+                    } else {
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]);
+                    }
+                    if (row < c_rows) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            int4 w;
+                            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[i], o[i + 1]), t1 = __floats2bfloat162_rn(o[i + 2], o[i + 3]);
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[i + 4], o[i + 5]), t3 = __floats2bfloat162_rn(o[i + 6], o[i + 7]);
+                            w.x = *reinterpret_cast<int*>(&t0);
+                            w.y = *reinterpret_cast<int*>(&t1);
+                            w.z = *reinterpret_cast<int*>(&t2);
+                            w.w = *reinterpret_cast<int*>(&t3);
+                            *reinterpret_cast<int4*>(crow + c + i) = w;
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[win]);
+                if (++win == 2) {
+                    win = 0;
+                    win_phase ^= 1;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && s_abort && p.error_flag != nullptr) atomicExch(p.error_flag, 1);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    }
+    return fn;
+}
+
+// 2-D row-major [rows, cols] tensor, box = 128 bytes of columns x box_rows rows, 128B swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const uint64_t esz = fp8 ? 1 : 2;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * esz};
+    cuuint32_t box[2] = {(cuuint32_t)(kKBlockBytes / esz), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int kBlockN, bool kFp8, bool kSwiGLU>
+cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
+    using C = Cfg<kBlockN, kFp8, kSwiGLU>;
+    CUtensorMap map_a, map_b;
+    const uint32_t b_box_rows = kSwiGLU ? kBlockN / 2 : kBlockN;
+    bool ok;
+    if (a.mode == 0) {
+        ok = make_map(&map_a, a.a, kFp8, (uint64_t)a.m_total, (uint64_t)a.k, kBlockM) &&
+             make_map(&map_b, a.b, kFp8, (uint64_t)a.num_groups * a.n, (uint64_t)a.k, b_box_rows);
+    } else {
+        ok = make_map(&map_a, a.a, kFp8, (uint64_t)a.n, (uint64_t)a.m_total, kBlockM) &&
+             make_map(&map_b, a.b, kFp8, (uint64_t)a.k, (uint64_t)a.m_total, b_box_rows);
+    }
+    if (!ok) return cudaErrorInvalidValue;
+    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kernel<<<a.num_sms, kNumThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
+    if (a.num_groups < 1 || a.num_groups > kMaxGroups || a.num_sms < 1) return cudaErrorInvalidValue;
+    if (a.m_total <= 0) return cudaSuccess;
+    const int kb = a.fp8 ? 128 : 64;
+    if (a.mode == 0) {
+        if (a.k % kb != 0) return cudaErrorInvalidValue;
+        if (a.fp8) {
+            if (a.a_scales == nullptr || a.b_scales == nullptr || a.k % 128 != 0) return cudaErrorInvalidValue;
+            if (a.swiglu) {
+                if ((a.n / 2) % 128 != 0) return cudaErrorInvalidValue;  // gate/up halves must start on scale-block boundaries
+                return launch_impl<128, true, true>(a, stream);
+            }
+            if (a.n % 128 != 0) return cudaErrorInvalidValue;
+            return launch_impl<128, true, false>(a, stream);
+        }
+        if (a.swiglu) {
+            if ((a.n / 2) % 128 == 0) return launch_impl<256, false, true>(a, stream);
+            if ((a.n / 2) % 64 == 0) return launch_impl<128, false, true>(a, stream);
+            return cudaErrorInvalidValue;
+        }
+        if (a.n % 256 == 0) return launch_impl<256, false, false>(a, stream);
+        if (a.n % 128 == 0) return launch_impl<128, false, false>(a, stream);
+        return cudaErrorInvalidValue;
+    }
+    // K-grouped (weight gradients), bf16 only
+    if (a.fp8 || a.swiglu || a.n % kBlockM != 0) return cudaErrorInvalidValue;
+    if (a.k % 256 == 0) return launch_impl<256, false, false>(a, stream);
+    if (a.k % 128 == 0) return launch_impl<128, false, false>(a, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace dx

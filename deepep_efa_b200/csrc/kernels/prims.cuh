@@ -160,7 +160,9 @@ __device__ __forceinline__ void fp8_scale_from_amax(float amax, bool round_pow2,
         inv_scale = 1.0f / scale;
     } else {
         scale = amax / kFp8Max;
-        inv_scale = kFp8Max / amax;
+        // 448 * (1 / amax), not 448 / amax: this is what `448.0 / tensor` evaluates to in PyTorch, and the
+        // one-ulp difference decides ties when rounding to e4m3.
+        inv_scale = kFp8Max * __frcp_rn(amax);
     }
 }
 

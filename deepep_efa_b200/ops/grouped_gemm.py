@@ -1,0 +1,56 @@
+"""Grouped expert GEMM (tcgen05 / TMEM / TMA kernel in csrc/kernels/grouped_gemm.cu) and its autograd wrapper.
+
+``grouped_gemm(a, b, m_offsets)`` computes ``c[m] = a[m] @ b[g].T`` for the rows m of expert g, where the rows of
+expert g are ``[m_offsets[g], m_offsets[g+1])`` and every boundary is a multiple of 128. Operands are bf16, or
+e4m3 with DeepSeek-style fp32 scales (1x128 on ``a``, 128x128 on ``b``). ``swiglu=True`` treats ``b`` as
+``[G, 2*I, K]`` = [gate; up] and returns ``silu(a @ gate.T) * (a @ up.T)``.
+
+The reference library ships no GEMM (its users run the expert FFN themselves); this exists for the fused MoE
+layer and the training path.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _ext
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, m_offsets: torch.Tensor, *, swiglu: bool = False,
+                 a_scales: Optional[torch.Tensor] = None, b_scales: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
+    """M-grouped GEMM; see the module docstring. Returns bf16 ``[M, N]`` (``[M, N/2]`` with ``swiglu``)."""
+    return _ext.load().grouped_gemm(a, b, m_offsets, 0, swiglu, a_scales, b_scales, out, num_sms)
+
+
+def grouped_gemm_wgrad(a_t: torch.Tensor, b_t: torch.Tensor, m_offsets: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                       num_sms: int = 0) -> torch.Tensor:
+    """K-grouped GEMM for weight gradients: ``c[g] = a_t[:, rows of g] @ b_t[:, rows of g].T`` with
+    ``a_t`` ``[N_out, M]`` and ``b_t`` ``[K_out, M]`` (both bf16, M contiguous). Returns bf16 ``[G, N_out, K_out]``."""
+    return _ext.load().grouped_gemm(a_t, b_t, m_offsets, 1, False, None, None, out, num_sms)
+
+
+def reference_grouped_gemm(a: torch.Tensor, b: torch.Tensor, m_offsets: torch.Tensor, swiglu: bool = False,
+                           a_scales: Optional[torch.Tensor] = None, b_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Plain PyTorch fp32 reference of :func:`grouped_gemm` (used by the tests)."""
+    G = m_offsets.numel() - 1
+    offs = m_offsets.tolist()
+    af = a.float()
+    if a_scales is not None:
+        af = (af.view(a.size(0), -1, 128) * a_scales.unsqueeze(-1)).view(a.shape)
+    K = a.size(1)
+    bf = b.float().view(G, -1, K)
+    if b_scales is not None:
+        N = bf.size(1)
+        bf = (bf.view(G, N // 128, 128, K // 128, 128) * b_scales.view(G, N // 128, 1, K // 128, 1)).view(G, N, K)
+    N = bf.size(1)
+    out = torch.zeros(a.size(0), N // 2 if swiglu else N, dtype=torch.float32, device=a.device)
+    for g in range(G):
+        r = slice(offs[g], offs[g + 1])
+        y = af[r] @ bf[g].t()
+        if swiglu:
+            gate, up = y[:, :N // 2], y[:, N // 2:]
+            y = torch.nn.functional.silu(gate) * up
+        out[r] = y
+    return out

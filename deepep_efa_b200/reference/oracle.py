@@ -217,6 +217,7 @@ def low_latency_dispatch(xs: Sequence[torch.Tensor], topk_idxs: Sequence[torch.T
             e = d * L + le
             for s in range(R):
                 if s in masked_ranks:
+                    outs[d]['layout_range'][le, s] = fill[d][le] << 32  # empty segment
                     continue
                 hits = (topk_idxs[s] == e).nonzero()  # row-major order = (token, k) order
                 toks = hits[:, 0]

@@ -1,0 +1,93 @@
+"""Grouped tcgen05 GEMM against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _offsets(rows, device="cuda"):
+    o = [0]
+    for r in rows:
+        o.append(o[-1] + r)
+    return torch.tensor(o, dtype=torch.int32, device=device)
+
+
+def _rel_err(x, ref):
+    return ((x.float() - ref).norm() / ref.norm().clamp(min=1e-12)).item()
+
+
+@pytest.mark.parametrize("rows,K,N", [([128], 64, 128), ([128, 256, 0, 384], 512, 256), ([256, 128], 1024, 384), ([128] * 5, 192, 512)])
+def test_bf16_mgrouped(rows, K, N):
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm, reference_grouped_gemm
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(0)
+    G, M = len(rows), sum(rows)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(G, N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    offs = _offsets(rows)
+    c = grouped_gemm(a, b, offs)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    ref = reference_grouped_gemm(a, b, offs)
+    assert _rel_err(c, ref) < 1e-2, _rel_err(c, ref)
+    # a second launch on a smaller persistent grid walks several tiles per CTA
+    c2 = grouped_gemm(a, b, offs, num_sms=3)
+    assert torch.equal(c, c2)
+
+
+@pytest.mark.parametrize("rows,K,I", [([128, 256], 256, 128), ([128, 128, 384], 512, 192)])
+def test_bf16_swiglu(rows, K, I):
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm, reference_grouped_gemm
+    torch.manual_seed(1)
+    G, M = len(rows), sum(rows)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(G, 2 * I, K, device="cuda") * 0.1).to(torch.bfloat16)
+    offs = _offsets(rows)
+    c = grouped_gemm(a, b, offs, swiglu=True)
+    assert c.shape == (M, I)
+    ref = reference_grouped_gemm(a, b, offs, swiglu=True)
+    assert _rel_err(c, ref) < 1.5e-2, _rel_err(c, ref)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_fp8_blockscaled(swiglu):
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm, reference_grouped_gemm
+    from deepep_efa_b200.reference import oracle
+    C = _ext.load()
+    torch.manual_seed(2)
+    rows, K, N = [128, 256, 128], 512, 256
+    G, M = len(rows), sum(rows)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    a, a_s = C.per_token_cast_to_fp8(x, False, False)
+    w = torch.randn(G, N, K, device="cuda") * 0.05
+    wb = w.view(G, N // 128, 128, K // 128, 128)
+    b_s = (wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0).contiguous()
+    b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn)
+    offs = _offsets(rows)
+    c = grouped_gemm(a, b, offs, swiglu=swiglu, a_scales=a_s, b_scales=b_s)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    ref = reference_grouped_gemm(a, b, offs, swiglu=swiglu, a_scales=a_s, b_scales=b_s)
+    assert _rel_err(c, ref) < 1e-2, _rel_err(c, ref)
+
+
+def test_bf16_wgrad_kgrouped():
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm_wgrad
+    torch.manual_seed(3)
+    rows, n_out, k_out = [128, 0, 256], 256, 128
+    M = sum(rows)
+    dy = torch.randn(M, n_out, device="cuda").to(torch.bfloat16)
+    x = torch.randn(M, k_out, device="cuda").to(torch.bfloat16)
+    offs = _offsets(rows)
+    dw = grouped_gemm_wgrad(dy.t().contiguous(), x.t().contiguous(), offs)
+    assert dw.shape == (3, n_out, k_out)
+    o = offs.tolist()
+    for g in range(3):
+        ref = dy[o[g]:o[g + 1]].float().t() @ x[o[g]:o[g + 1]].float()
+        if rows[g] == 0:
+            assert dw[g].float().abs().max().item() == 0
+        else:
+            assert _rel_err(dw[g], ref) < 1e-2

@@ -1,0 +1,359 @@
+"""Headline benchmark: low-latency dispatch + combine latency, plus normal-mode NVLink bandwidth.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Headline metric (lower is better): microseconds for one low-latency ``dispatch`` followed by one
+``combine`` with 128 tokens per rank, hidden 7168, 256 experts, top-8, FP8 dispatch / BF16 combine — the
+reference's tests/test_low_latency.py protocol (:245-251): inputs stay on the device, an L2 flush (256 MB
+write) runs between iterations outside the timed events, every iteration is timed with CUDA events on the
+launching stream, and the job-wide number is the MAX over ranks of the per-rank mean.
+
+Also reported: the normal-mode FP8 dispatch / BF16 combine bandwidth (4096 tokens per rank, reference byte
+definitions, tests/test_intranode.py:186-214) and an end-to-end number that moves each step's inputs from
+pinned host memory and reads the step's result back.
+
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...``.
+Synthetic data: N(0,1) activations, uniform top-8 without replacement, softmax weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LL_TOKENS, HIDDEN, NUM_EXPERTS, TOPK = 128, 7168, 256, 8
+NORMAL_TOKENS = 4096
+PUBLISHED_LL_US = 1145.0  # reference README.md:83, EP16 on 2 nodes (no single-node number is published)
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int, period_ms: int = 20):
+        self.gpu_index, self.period_ms = gpu_index, period_ms
+        self.proc, self.path = None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return res
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1])), smax.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            res.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        return res
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v for v in vis.split(",") if v != ""]
+        try:
+            return int(ids[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------------
+def init_dist(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == n_gpus, f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n_gpus}"
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    return rank, world, local_rank
+
+
+def max_over_ranks(value: float) -> float:
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed_loop(fn, steps: int, flush: torch.Tensor):
+    """K iterations, each [L2 flush][event][fn][event]; returns the mean milliseconds per iteration."""
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    dist.barrier()
+    torch.cuda.synchronize()
+    for i in range(steps):
+        flush.zero_()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    return sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / steps
+
+
+def make_inputs(rank: int, tokens: int, masked_fraction: float = 0.0):
+    g = torch.Generator(device="cpu").manual_seed(rank)
+    x = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16)
+    topk_idx = torch.rand(tokens, NUM_EXPERTS, generator=g).topk(TOPK, dim=-1).indices.to(torch.int64)
+    topk_w = torch.softmax(torch.randn(tokens, TOPK, generator=g), dim=-1).float()
+    if masked_fraction > 0:
+        topk_idx[torch.rand(tokens, TOPK, generator=g) < masked_fraction] = -1
+    return x, topk_idx, topk_w
+
+
+# ------------------------------------------------------------------------------------------------
+# this library
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import deepep_efa_b200 as ep
+    from deepep_efa_b200.reference import oracle
+
+    rank, world, local_rank = init_dist(args.gpus)
+    group = dist.group.WORLD
+    steps, warmup = args.steps, max(args.warmup, 3)
+    ll_bytes = ep.Buffer.get_low_latency_rdma_size_hint(LL_TOKENS, HIDDEN, world, NUM_EXPERTS)
+    nvl_bytes = ep.Config(32, 6, 256, 6, 128).get_nvl_buffer_size_hint(HIDDEN * 2, world, NORMAL_TOKENS) if not args.skip_normal else (2 << 20)
+    buf = ep.Buffer(group, num_nvl_bytes=nvl_bytes, num_rdma_bytes=ll_bytes, low_latency_mode=True, explicitly_destroy=True)
+    flush = torch.empty(256 << 20, dtype=torch.int8, device="cuda")
+
+    # ---------------- low-latency dispatch + combine (headline) ----------------
+    x_h, idx_h, w_h = make_inputs(rank, LL_TOKENS)
+    x, topk_idx, topk_w = x_h.cuda(), idx_h.cuda(), w_h.cuda()
+    L = NUM_EXPERTS // world
+    sim_gemm_out = torch.randn(L, world * LL_TOKENS, HIDDEN, device="cuda").to(torch.bfloat16) * 0.1
+    out = torch.empty(LL_TOKENS, HIDDEN, dtype=torch.bfloat16, device="cuda")
+
+    def ll_step():
+        _, _, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+        buf.low_latency_combine(sim_gemm_out, topk_idx, topk_w, handle, out=out)
+
+    # correctness of exactly what is timed: combine(dispatch(x)) == x * sum(w) through the FP8 wire format
+    (px, ps), cnt, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+    back = oracle.per_token_cast_back(px.view(-1, HIDDEN), ps.view(-1, HIDDEN // 128)).view(px.shape)
+    chk, _, _ = buf.low_latency_combine(back, topk_idx, topk_w, handle)
+    torch.cuda.synchronize()
+    buf.check_status()
+    diff = oracle.calc_diff(x.float() * topk_w.sum(1, keepdim=True), chk.float())
+    assert diff < 9e-4, f"low-latency round trip is wrong: diff={diff}"
+
+    for _ in range(warmup):
+        ll_step()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ll_ms = timed_loop(ll_step, steps, flush)
+    clocks = sampler.stop()
+    buf.check_status(sync=True)
+    ll_us = max_over_ranks(ll_ms * 1e3)
+
+    # separate dispatch / combine times (same protocol)
+    state = {}
+
+    def ll_dispatch_only():
+        state["h"] = buf.low_latency_dispatch(x, topk_idx, LL_TOKENS, NUM_EXPERTS, use_fp8=True)[2]
+
+    def ll_combine_only():
+        buf.low_latency_combine(sim_gemm_out, topk_idx, topk_w, state["h"], out=out)
+
+    sub_steps = max(10, min(steps, 200))
+    disp_us = comb_us = None
+    if not args.skip_breakdown:
+        # dispatch and combine alternate on the wire; time each half with its own events
+        d_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(sub_steps)]
+        c_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(sub_steps)]
+        dist.barrier()
+        torch.cuda.synchronize()
+        for i in range(sub_steps):
+            flush.zero_()
+            d_ev[i][0].record(); ll_dispatch_only(); d_ev[i][1].record()
+            c_ev[i][0].record(); ll_combine_only(); c_ev[i][1].record()
+        torch.cuda.synchronize()
+        disp_us = max_over_ranks(sum(a.elapsed_time(b) for a, b in d_ev) / sub_steps * 1e3)
+        comb_us = max_over_ranks(sum(a.elapsed_time(b) for a, b in c_ev) / sub_steps * 1e3)
+
+    # ---------------- end to end: pinned host inputs in, result out, every step ----------------
+    x_p, idx_p, w_p = x_h.pin_memory(), idx_h.pin_memory(), w_h.pin_memory()
+    out_p = torch.empty(LL_TOKENS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    x_d, idx_d, w_d = torch.empty_like(x), torch.empty_like(topk_idx), torch.empty_like(topk_w)
+
+    def e2e_step():
+        x_d.copy_(x_p, non_blocking=True)
+        idx_d.copy_(idx_p, non_blocking=True)
+        w_d.copy_(w_p, non_blocking=True)
+        _, _, h, _, _ = buf.low_latency_dispatch(x_d, idx_d, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+        o, _, _ = buf.low_latency_combine(sim_gemm_out, idx_d, w_d, h, out=out)
+        out_p.copy_(o, non_blocking=True)
+
+    for _ in range(warmup):
+        e2e_step()
+    e2e_us = max_over_ranks(timed_loop(e2e_step, steps, flush) * 1e3)
+    h2d = x_p.numel() * 2 + idx_p.numel() * 8 + w_p.numel() * 4
+    d2h = out_p.numel() * 2
+    buf.check_status(sync=True)
+
+    # ---------------- masked-slot sweep (2 % / 5 % of the top-k slots are -1) ----------------
+    masked = {}
+    if not args.skip_breakdown:
+        for frac in (0.02, 0.05):
+            _, mi, mw = make_inputs(rank, LL_TOKENS, frac)
+            mi, mw = mi.cuda(), mw.cuda()
+
+            def masked_step():
+                _, _, h, _, _ = buf.low_latency_dispatch(x, mi, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+                buf.low_latency_combine(sim_gemm_out, mi, mw, h, out=out)
+
+            for _ in range(3):
+                masked_step()
+            masked[f"{int(frac * 100)}pct"] = round(max_over_ranks(timed_loop(masked_step, sub_steps, flush) * 1e3), 2)
+
+    # ---------------- normal mode: FP8 dispatch / BF16 combine bandwidth ----------------
+    normal = None
+    if not args.skip_normal:
+        normal = bench_normal(buf, rank, world, flush, max(10, min(steps, 50)), warmup)
+
+    result = {
+        "metric": "ll_dispatch_combine_us",
+        "value": round(ll_us, 3),
+        "unit": "us",
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": round(ll_us / 1e3, 6),
+        "higher_is_better": False,
+        "scaling": "weak",
+        "vs_baseline": round(ll_us / PUBLISHED_LL_US, 5),
+        "dtype": "fp8_e4m3 dispatch / bf16 combine",
+        "data": "synthetic: N(0,1) bf16 activations, uniform top-8 of 256 experts without replacement, softmax weights",
+        "config": {"model": "low-latency EP dispatch+combine", "tokens_per_rank": LL_TOKENS, "global_batch": LL_TOKENS * world,
+                   "seq_len": 1, "hidden": HIDDEN, "num_experts": NUM_EXPERTS, "topk": TOPK, "parallelism": f"ep{world}",
+                   "l2": "256 MB flush between timed iterations", "timing": "CUDA events per iteration, max over ranks"},
+        "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
+                   "samples": clocks["samples"]},
+        "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 2 * steps,
+        "ll_dispatch_us": None if disp_us is None else round(disp_us, 2),
+        "ll_combine_us": None if comb_us is None else round(comb_us, 2),
+        "ll_masked_us": masked,
+        "normal": normal,
+        "impl": "deepep_efa_b200",
+    }
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+    buf.destroy()
+    dist.destroy_process_group()
+
+
+def bench_normal(buf, rank, world, flush, steps, warmup):
+    """Normal-mode dispatch (BF16 in, FP8 on the wire, quantised inside the dispatch kernel) and BF16 combine."""
+    import deepep_efa_b200 as ep
+
+    x_h, idx_h, w_h = make_inputs(rank + 100, NORMAL_TOKENS)
+    x, topk_idx, topk_w = x_h.cuda(), idx_h.cuda(), w_h.cuda()
+    per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(topk_idx, NUM_EXPERTS)
+    state = {}
+
+    def do_dispatch():
+        state["r"] = buf.dispatch(x, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert,
+                                  topk_idx=topk_idx, topk_weights=topk_w, quantize_fp8=True)
+
+    do_dispatch()
+    (rx, rs), _, _, _, handle, _ = state["r"]
+    n_recv = rx.size(0)
+    y = buf.empty_symmetric([n_recv, HIDDEN], torch.bfloat16)
+    y.normal_()
+
+    def do_cached_dispatch():
+        state["c"] = buf.dispatch(x, handle=handle, quantize_fp8=True)
+
+    def do_combine():
+        state["o"] = buf.combine(y, handle)
+
+    res = {}
+    for name, fn in (("dispatch_fp8", do_dispatch), ("dispatch_fp8_cached", do_cached_dispatch), ("combine_bf16", do_combine)):
+        for _ in range(warmup):
+            fn()
+        ms = max_over_ranks(timed_loop(fn, steps, flush))
+        nbytes = n_recv * HIDDEN * 2
+        if name.startswith("dispatch"):
+            nbytes = nbytes * (1 + 4 / 128) / 2
+        res[name] = {"ms": round(ms, 4), "GBps": round(nbytes / 1e9 / (ms / 1e3), 1)}
+    buf.check_status(sync=True)
+    res["recv_tokens"] = int(n_recv)
+    res["bytes_definition"] = "recv_x.numel()*2 (x(1+4/128)/2 for FP8), all source ranks including self"
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm
+# ------------------------------------------------------------------------------------------------
+def run_reference(args):
+    from baseline import reference_arm
+    reference_arm.main(args)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-normal", action="store_true")
+    ap.add_argument("--skip-breakdown", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

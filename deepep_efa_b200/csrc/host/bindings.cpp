@@ -603,6 +603,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("status_code", [](Runtime& r) { return r.core->status_code(); })
         .def("status_string", [](Runtime& r) { return r.core->status_string(); })
         .def("clear_status", [](Runtime& r) { r.core->clear_status(); })
+        .def("enable_trace", [](Runtime& r, bool on) { r.core->enable_trace(on); })
+        .def("read_trace", [](Runtime& r) { return r.core->read_trace(); })
         .def("reset_control", [](Runtime& r) { r.core->reset_control(); })
         .def("release", [](Runtime& r) { r.core->release(); })
         .def("is_available", [](Runtime& r) { return r.core->available(); })

@@ -153,6 +153,8 @@ class RuntimeCore {
         if (local_scratch_) cudaFree(local_scratch_);
         if (local_seq_) cudaFree(local_seq_);
         if (never_set_flag_) cudaFree(never_set_flag_);
+        if (trace_) cudaFree(trace_);
+        trace_ = nullptr;
         if (host_) cudaFreeHost((void*)host_);
         base_ = nullptr;
         available_ = false;
@@ -166,6 +168,7 @@ class RuntimeCore {
         c.status = &host_dev_->status;
         c.local_scratch = local_scratch_;
         c.seq = local_seq_;
+        c.trace = trace_;
         c.timeout_cycles = timeout_cycles_;
         c.mask_on_timeout = mask_on_timeout_ ? 1 : 0;
         return c;
@@ -254,6 +257,29 @@ class RuntimeCore {
         }
     }
 
+    // ---- tracing -------------------------------------------------------------------------------
+    // Kernels stamp the GPU global timer at phase boundaries of their first and last CTA.
+    void enable_trace(bool on) {
+        DX_CUDA_CHECK(cudaSetDevice(device_));
+        if (on && trace_ == nullptr) {
+            DX_CUDA_CHECK(cudaMalloc(&trace_, kTraceWords * sizeof(unsigned long long)));
+            DX_CUDA_CHECK(cudaMemset(trace_, 0, kTraceWords * sizeof(unsigned long long)));
+        } else if (!on && trace_ != nullptr) {
+            DX_CUDA_CHECK(cudaDeviceSynchronize());
+            cudaFree(trace_);
+            trace_ = nullptr;
+        }
+    }
+    std::vector<unsigned long long> read_trace() {
+        std::vector<unsigned long long> v(kTraceWords, 0);
+        if (trace_ != nullptr) {
+            DX_CUDA_CHECK(cudaSetDevice(device_));
+            DX_CUDA_CHECK(cudaDeviceSynchronize());
+            DX_CUDA_CHECK(cudaMemcpy(v.data(), trace_, kTraceWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        }
+        return v;
+    }
+
     int status_code() const { return read_word(&host_->status.code); }
     std::string status_string() const {
         const int code = read_word(&host_->status.code), rank = read_word(&host_->status.rank);
@@ -331,6 +357,8 @@ class RuntimeCore {
     int* local_scratch_ = nullptr;
     uint64_t* local_seq_ = nullptr;
     uint64_t* never_set_flag_ = nullptr;
+    unsigned long long* trace_ = nullptr;
+    static constexpr int kTraceWords = dx::kNumFamilies * 2 * dx::kTraceStampsPerSlot;
     HostWords* host_ = nullptr;
     HostWords* host_dev_ = nullptr;
     int clock_khz_ = 1965000;

@@ -57,7 +57,6 @@ __global__ void __launch_bounds__(kNotifyThreads, 1) notify_kernel(const __grid_
         }
         __syncthreads();
         if (tid < R) {
-            fence_acq_rel_sys();
             st_release_sys(&c.ctrl(tid)->notify_seq[me], seq);
             if (!wait_ge_sys(&c.my_ctrl()->notify_seq[tid], seq, c.timeout_cycles)) {
                 report(c.status, kTimeoutNotify, me, tid, 0);
@@ -144,7 +143,6 @@ __global__ void __launch_bounds__(kNotifyThreads, 1) notify_kernel(const __grid_
     }
     __syncthreads();
     if (tid == 0) {
-        fence_acq_rel_sys();
         mailbox_post(c, kMbChanPrefix, d, nullptr, 0, seq);
     }
     if (cta_is_last(c.local_scratch + kTicketNotify, gridDim.x) && tid == 0) commit_seq(c, kFamNotify, seq);
@@ -344,7 +342,6 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const __g
     // ---- completion: when my last CTA is done, tell every peer; CTA 0 waits for every peer ----
     if (cta_is_last(c.local_scratch + kTicketDispatch, gridDim.x)) {
         if (tid < R) {
-            fence_acq_rel_sys();
             st_release_sys(&c.ctrl(tid)->barrier_in[kBarDispatch][me], seq);
         }
         if (tid == 0) commit_seq(c, kFamDispatch, seq);
@@ -468,7 +465,6 @@ __global__ void __launch_bounds__(kCombineThreads, 1) combine_kernel(const __gri
     // "my expert outputs are final and live at this offset" -> every home rank
     if (blockIdx.x == 0 && tid < R) {
         uint64_t w[2] = {a.x_off, a.topk_w_off};
-        fence_acq_rel_sys();
         mailbox_post(c, kMbCombineSrc, tid, w, 2, seq);
     }
     if (tid < R) {
@@ -495,7 +491,6 @@ __global__ void __launch_bounds__(kCombineThreads, 1) combine_kernel(const __gri
     // Peers may reuse their expert-output buffers only after every home rank has finished reading.
     if (cta_is_last(c.local_scratch + kTicketCombine, gridDim.x)) {
         if (tid < R) {
-            fence_acq_rel_sys();
             st_release_sys(&c.ctrl(tid)->barrier_in[kBarCombine][me], seq);
         }
         if (tid == 0) commit_seq(c, kFamCombine, seq);

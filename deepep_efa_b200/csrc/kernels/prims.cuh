@@ -195,6 +195,15 @@ __device__ __forceinline__ void commit_seq(const RankCtx& c, int fam, uint64_t s
     *reinterpret_cast<volatile uint64_t*>(c.seq + fam) = seq;
 }
 
+// Phase time stamp (nanoseconds of the GPU's global timer) for the tracing facility; free when tracing is off.
+__device__ __forceinline__ void trace_stamp(const RankCtx& c, int fam, int slot, int idx) {
+    if (c.trace != nullptr && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        c.trace[(fam * 2 + slot) * kTraceStampsPerSlot + idx] = t;
+    }
+}
+
 // Posts `n` payload words + a sequence number into `dst`'s mailbox slot [kind][me]. One thread.
 __device__ __forceinline__ void mailbox_post(const RankCtx& c, int kind, int dst, const uint64_t* words, int n, uint64_t seq) {
     Mailbox* mb = &c.ctrl(dst)->mailbox[kind][c.rank];
@@ -221,7 +230,6 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankCtx& c, uint64_t seq)
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < c.num_ranks) {
-        fence_acq_rel_sys();
         st_release_sys(&c.ctrl(threadIdx.x)->barrier_in[kBarExplicit][c.rank], seq);
         if (!wait_ge_sys(&c.my_ctrl()->barrier_in[kBarExplicit][threadIdx.x], seq, c.timeout_cycles)) {
             report(c.status, kTimeoutBarrier, c.rank, threadIdx.x, (int)seq);
@@ -235,15 +243,17 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankCtx& c, uint64_t seq)
 // Grid-wide "everyone is done" detection for one rank's slice of a launch (gridDim.x CTAs).
 // Returns true in exactly one CTA: the last one to arrive. `ticket` is zero between kernels.
 __device__ __forceinline__ bool cta_is_last(int* ticket, int num_ctas) {
+    // GPU scope is enough: the ticket is rank-local. A caller that publishes to peers afterwards does so
+    // with a system-scope release, which is cumulative over everything ordered before it here.
     __shared__ int s_last;
     __syncthreads();
     if (threadIdx.x == 0) {
-        fence_acq_rel_sys();
+        fence_acq_rel_gpu();
         const int old = atomicAdd(ticket, 1);
         s_last = (old == num_ctas - 1);
         if (s_last) {
             *ticket = 0;
-            fence_acq_rel_sys();
+            fence_acq_rel_gpu();
         }
     }
     __syncthreads();

@@ -87,6 +87,7 @@ struct RankCtx {
     StatusBlock* status;         // mapped host memory
     int* local_scratch;          // small rank-local device scratch (tickets), zero between kernels
     uint64_t* seq;               // rank-local device memory: last finished sequence of every kernel family
+    unsigned long long* trace;   // optional device buffer for phase time stamps (nullptr = tracing off)
     long long timeout_cycles;
     int mask_on_timeout;         // low-latency shrink mode: a rank that times out is masked instead of failing the call
 
@@ -101,6 +102,8 @@ struct RankCtx {
 };
 
 // Kernel families; each has its own monotonically growing sequence number on every rank.
+constexpr int kTraceStampsPerSlot = 16;  // trace layout: [family][slot 0 = first CTA, 1 = last CTA][stamp]
+
 enum Family : int { kFamNotify = 0, kFamDispatch = 1, kFamCombine = 2, kFamBarrier = 3, kFamLLDispatch = 4, kFamLLCombine = 5, kNumFamilies = 8 };
 
 }  // namespace dx

@@ -1,0 +1,146 @@
+"""Real multi-process runs: one process per GPU, CUDA IPC peer mappings, NCCL only for bootstrap.
+Skipped when fewer than two GPUs are visible. Every rank checks its own outputs against the pure-PyTorch
+oracle evaluated on the all-gathered inputs."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import traceback
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import deepep_efa_b200 as ep
+        from deepep_efa_b200.reference import oracle
+        from helpers import make_routing, make_tokens
+
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+
+        T, H, E, K = 96, 2048, 8 * world, 4
+        L = E // world
+        buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=128 << 20,
+                        num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(T, H, world, E), low_latency_mode=True,
+                        explicitly_destroy=True, timeout_ms=5000)
+        x = make_tokens(T, H, "cuda", seed=rank)
+        idx, w = make_routing(T, E, K, "cuda", seed=rank, masked_fraction=0.05)
+        all_x = [t.cpu() for t in gather(x.cpu())]
+        all_idx = [t.cpu() for t in gather(idx.cpu())]
+        all_w = [t.cpu() for t in gather(w.cpu())]
+
+        for it in range(3):
+            # ---- normal mode, bf16 and fused fp8 ----
+            per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(idx, E)
+            for fused in (False, True):
+                recv_x, recv_idx, recv_w, counts, handle, ev = buf.dispatch(
+                    x, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert,
+                    topk_idx=idx, topk_weights=w, quantize_fp8=fused, async_finish=(it == 1))
+                ev.current_stream_wait()
+                torch.cuda.synchronize()
+                buf.check_status()
+                if fused:
+                    pairs = [oracle.per_token_cast_to_fp8(t) for t in all_x]
+                    ref = oracle.dispatch([p[0] for p in pairs], all_idx, all_w, E, x_scales=[p[1] for p in pairs])[rank]
+                    assert torch.equal(recv_x[0].cpu().view(torch.uint8), ref["recv_x"].view(torch.uint8))
+                    assert torch.equal(recv_x[1].cpu(), ref["recv_x_scales"])
+                    y = oracle.per_token_cast_back(recv_x[0].cpu(), recv_x[1].cpu()).cuda()
+                else:
+                    ref = oracle.dispatch(all_x, all_idx, all_w, E)[rank]
+                    assert torch.equal(recv_x.cpu(), ref["recv_x"])
+                    y = recv_x
+                assert torch.equal(recv_idx.cpu(), ref["recv_topk_idx"]) and torch.equal(recv_w.cpu(), ref["recv_topk_weights"])
+                assert counts == ref["num_recv_tokens_per_expert_list"]
+                assert torch.equal(handle[0].cpu(), ref["rank_prefix_matrix"])
+                out, out_w, _ = buf.combine(y, handle, topk_weights=recv_w)
+                torch.cuda.synchronize()
+                buf.check_status()
+                hits = in_rank.sum(dim=1, keepdim=True).float()
+                base = y.float() if False else None
+                if fused:
+                    want = oracle.per_token_cast_back(*oracle.per_token_cast_to_fp8(x.cpu())).float().cuda() * hits
+                    assert oracle.calc_diff(want, out.float()) < 1e-4
+                else:
+                    assert oracle.calc_diff(x.float() * hits, out.float()) < 5e-6
+                assert (out_w - w.masked_fill(idx == -1, 0)).abs().max() < 1e-6
+            # cached handle
+            rx2, *_ = buf.dispatch(x, handle=handle)
+            assert torch.equal(rx2.cpu(), oracle.dispatch(all_x, all_idx, all_w, E)[rank]["recv_x"])
+
+            # ---- low latency ----
+            for use_fp8 in (True, False):
+                stats = torch.zeros(L, dtype=torch.int32, device="cuda")
+                rx, cnt, h, _, hook = buf.low_latency_dispatch(x, idx, T, E, use_fp8=use_fp8, cumulative_local_expert_recv_stats=stats,
+                                                               return_recv_hook=(it == 2))
+                if hook is not None:
+                    hook()
+                torch.cuda.synchronize()
+                buf.check_status()
+                ref = oracle.low_latency_dispatch(all_x, all_idx, T, E, use_fp8)[rank]
+                assert torch.equal(cnt.cpu(), ref["packed_recv_count"]) and torch.equal(h[1].cpu(), ref["layout_range"])
+                for le in range(L):
+                    n = int(cnt[le])
+                    assert torch.equal(h[0][le, :n].cpu(), ref["src_info"][le, :n])
+                    if use_fp8:
+                        assert torch.equal(rx[0][le, :n].cpu().view(torch.uint8), ref["packed_recv_x"][le, :n].view(torch.uint8))
+                        assert torch.equal(rx[1][le, :n].cpu(), ref["packed_recv_x_scales"][le, :n])
+                    else:
+                        assert torch.equal(rx[le, :n].cpu(), ref["packed_recv_x"][le, :n])
+                if use_fp8:
+                    ysim = oracle.per_token_cast_back(rx[0].view(-1, H), rx[1].view(-1, H // 128)).view(rx[0].shape)
+                else:
+                    ysim = rx.clone()
+                o, _, hook = buf.low_latency_combine(ysim, idx, w, h, return_recv_hook=(it == 2))
+                if hook is not None:
+                    hook()
+                torch.cuda.synchronize()
+                buf.check_status()
+                want = x.float() * w.masked_fill(idx == -1, 0).sum(dim=1, keepdim=True)
+                assert oracle.calc_diff(want, o.float()) < (9e-4 if use_fp8 else 1e-5)
+        buf.destroy()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multiprocess_against_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = []
+    try:
+        for _ in procs:
+            res.append(q.get(timeout=240))
+    finally:
+        for p in procs:
+            p.join(20)
+            if p.is_alive():
+                p.terminate()
+    for rank, msg in res:
+        assert msg == "ok", f"rank {rank}: {msg}"

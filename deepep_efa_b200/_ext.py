@@ -31,6 +31,7 @@ CUDA_SOURCES = [
     "kernels/fp8_cast.cu",
     "kernels/ll.cu",
     "kernels/grouped_gemm.cu",
+    "kernels/permute.cu",
     "kernels/noalloc.cu",
 ]
 CPP_SOURCES = [

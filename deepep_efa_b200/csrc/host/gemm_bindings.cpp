@@ -116,6 +116,49 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     return c;
 }
 
+// dst[m] = scale[m] * src[src_row[m]]; rows of any dtype whose byte size is a multiple of 16
+torch::Tensor gather_rows(const torch::Tensor& src, const torch::Tensor& src_row, c10::optional<torch::Tensor> scale,
+                          c10::optional<torch::Tensor> out) {
+    DXG_CHECK(src.is_cuda() && src.dim() == 2 && src.is_contiguous(), "src must be a contiguous CUDA matrix");
+    DXG_CHECK(src_row.scalar_type() == torch::kInt32 && src_row.is_contiguous() && src_row.dim() == 1, "src_row must be int32 [M]");
+    const int64_t M = src_row.numel();
+    const int64_t row_bytes = src.size(1) * src.element_size();
+    DXG_CHECK(row_bytes % 16 == 0, "row size must be a multiple of 16 bytes");
+    c10::cuda::CUDAGuard guard(src.device());
+    torch::Tensor dst = out.has_value() ? *out : torch::empty({M, src.size(1)}, src.options());
+    DXG_CHECK(dst.is_contiguous() && dst.scalar_type() == src.scalar_type() && dst.size(0) == M && dst.size(1) == src.size(1), "out has the wrong shape");
+    const float* sc = nullptr;
+    if (scale.has_value()) {
+        DXG_CHECK(src.scalar_type() == torch::kBFloat16 && scale->scalar_type() == torch::kFloat32 && scale->numel() == M && scale->is_contiguous(), "scale needs bf16 rows and f32 [M]");
+        sc = scale->data_ptr<float>();
+    }
+    const cudaError_t e = dx::launch_gather_rows(src.data_ptr(), dst.data_ptr(), src_row.data_ptr<int>(), sc, (int)M, (int)row_bytes,
+                                                 at::cuda::getCurrentCUDAStream(src.device().index()).stream());
+    if (e != cudaSuccess) throw std::runtime_error(std::string("gather_rows: ") + cudaGetErrorString(e));
+    return dst;
+}
+
+// dst[n] = sum_k w[n,k] * src[pos[n,k]]
+torch::Tensor gather_reduce_rows(const torch::Tensor& src, const torch::Tensor& pos, c10::optional<torch::Tensor> w,
+                                 c10::optional<torch::Tensor> out) {
+    DXG_CHECK(src.is_cuda() && src.dim() == 2 && src.is_contiguous() && src.scalar_type() == torch::kBFloat16, "src must be contiguous bf16 [M,H]");
+    DXG_CHECK(pos.scalar_type() == torch::kInt32 && pos.is_contiguous() && pos.dim() == 2 && pos.size(1) <= 32, "pos must be int32 [N,K], K <= 32");
+    const int64_t N = pos.size(0), K = pos.size(1), H = src.size(1);
+    DXG_CHECK(H % 8 == 0, "hidden must be a multiple of 8");
+    c10::cuda::CUDAGuard guard(src.device());
+    torch::Tensor dst = out.has_value() ? *out : torch::empty({N, H}, src.options());
+    DXG_CHECK(dst.is_contiguous() && dst.scalar_type() == torch::kBFloat16 && dst.size(0) == N && dst.size(1) == H, "out has the wrong shape");
+    const float* wp = nullptr;
+    if (w.has_value()) {
+        DXG_CHECK(w->scalar_type() == torch::kFloat32 && w->is_contiguous() && w->numel() == N * K, "w must be f32 [N,K]");
+        wp = w->data_ptr<float>();
+    }
+    const cudaError_t e = dx::launch_gather_reduce_rows(src.data_ptr(), dst.data_ptr(), pos.data_ptr<int>(), wp, (int)N, (int)K, (int)H,
+                                                        at::cuda::getCurrentCUDAStream(src.device().index()).stream());
+    if (e != cudaSuccess) throw std::runtime_error(std::string("gather_reduce_rows: ") + cudaGetErrorString(e));
+    return dst;
+}
+
 int gemm_error(int device) { return error_flag(device).item<int>(); }
 void gemm_clear_error(int device) { error_flag(device).zero_(); }
 
@@ -125,6 +168,8 @@ void bind_gemm(py::module_& m) {
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
           py::arg("timeout_ms") = 2000.0);
+    m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
+    m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());
     m.def("gemm_error", &gemm_error);
     m.def("gemm_clear_error", &gemm_clear_error);
 }

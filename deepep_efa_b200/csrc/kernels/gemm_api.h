@@ -42,4 +42,12 @@ struct GroupedGemmArgs {
 // Returns cudaErrorInvalidValue for unsupported shapes (divisibility rules are in grouped_gemm.cu).
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& args, cudaStream_t stream);
 
+// Row gathers between receive order and the expert-major, 128-row-aligned layout (permute.cu).
+//   dst[m] = scale[m] * src[src_row[m]]   (src_row[m] < 0 -> zero row; scale may be null; bf16 rows when scaled)
+cudaError_t launch_gather_rows(const void* src, void* dst, const int* src_row, const float* scale, int num_dst_rows, int row_bytes,
+                               cudaStream_t stream);
+//   dst[n] = sum_k w[n,k] * src[pos[n,k]]  (bf16 rows, fp32 accumulate; pos < 0 skipped; w may be null = 1)
+cudaError_t launch_gather_reduce_rows(const void* src, void* dst, const int* pos, const float* w, int num_dst_rows, int num_k, int hidden,
+                                      cudaStream_t stream);
+
 }  // namespace dx

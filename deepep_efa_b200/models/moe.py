@@ -1,0 +1,202 @@
+"""Expert-parallel MoE layer on top of ``Buffer``: gate -> layout -> dispatch -> grouped expert GEMMs (SwiGLU FFN)
+-> weighted un-permute -> combine, with autograd.
+
+Two execution paths share the structure:
+
+* **training (BF16)**: every stage is an autograd function. The backward of dispatch is a combine and the backward
+  of combine is a cached-handle dispatch (deep_ep/buffer.py:512-519 documents that contract for the reference); the
+  expert GEMMs use the grouped tcgen05 kernel for forward, input gradients (transposed weights) and weight
+  gradients (K-grouped mode).
+* **inference (FP8)**: ``forward_fp8`` quantises inside the dispatch kernel, runs block-scaled FP8 grouped GEMMs
+  with the SwiGLU fused into the first GEMM's epilogue, and combines in BF16 (DeepSeek-V3-shaped experts).
+
+The reference is a communication library only and has no model code; this module is the model-side user of the
+API that the benchmark configurations (fused MoE forward, MoE training step) call for.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import grouped_gemm as gg
+from ..ops.permute import build_expert_plan, gather_rows, permute, unpermute_weighted
+
+EXPERT_ALIGNMENT = 128
+
+
+@dataclass
+class MoEConfig:
+    hidden: int
+    intermediate: int
+    num_experts: int
+    num_topk: int
+    init_std: float = 0.02
+    router_dtype: torch.dtype = torch.float32
+
+
+# ---------------------------------------------------------------------------------------------------------
+# communication autograd functions
+# ---------------------------------------------------------------------------------------------------------
+class _Dispatch(torch.autograd.Function):
+    """x [T,H], topk_weights [T,K] -> recv_x [N,H], recv_topk_weights [N,K]; routing outputs ride on ``ctx_out``."""
+
+    @staticmethod
+    def forward(ctx, x, topk_weights, topk_idx, buffer, num_experts, ctx_out):
+        per_rank, _, per_expert, in_rank, _ = buffer.get_dispatch_layout(topk_idx, num_experts)
+        recv_x, recv_idx, recv_w, counts, handle, _ = buffer.dispatch(
+            x, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert, topk_idx=topk_idx,
+            topk_weights=topk_weights, expert_alignment=EXPERT_ALIGNMENT)
+        ctx.buffer, ctx.handle = buffer, handle
+        ctx_out["recv_topk_idx"], ctx_out["counts"], ctx_out["handle"] = recv_idx, counts, handle
+        ctx.mark_non_differentiable(recv_idx)
+        return recv_x, recv_w
+
+    @staticmethod
+    def backward(ctx, grad_recv_x, grad_recv_w):
+        gx, gw, _ = ctx.buffer.combine(grad_recv_x.contiguous(), ctx.handle,
+                                       topk_weights=None if grad_recv_w is None else grad_recv_w.contiguous())
+        return gx, gw, None, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y_recv, buffer, handle):
+        ctx.buffer, ctx.handle = buffer, handle
+        out, _, _ = buffer.combine(y_recv, handle)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        g, *_ = ctx.buffer.dispatch(grad_out.contiguous(), handle=ctx.handle)
+        return g, None, None
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """y[m] = x[m] @ w[g].T for the rows m of expert g (w: [G, N, K])."""
+
+    @staticmethod
+    def forward(ctx, x, w, m_offsets):
+        ctx.save_for_backward(x, w, m_offsets)
+        if x.is_cuda:
+            return gg.grouped_gemm(x, w, m_offsets)
+        return gg.reference_grouped_gemm(x, w, m_offsets).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x, w, m_offsets = ctx.saved_tensors
+        grad = grad.contiguous()
+        if x.is_cuda:
+            dx = gg.grouped_gemm(grad, w.transpose(1, 2).contiguous(), m_offsets)
+            dw = gg.grouped_gemm_wgrad(grad.t().contiguous(), x.t().contiguous(), m_offsets)
+        else:
+            dx = gg.reference_grouped_gemm(grad, w.transpose(1, 2).contiguous(), m_offsets).to(x.dtype)
+            offs = m_offsets.tolist()
+            dw = torch.stack([grad[offs[g]:offs[g + 1]].float().t() @ x[offs[g]:offs[g + 1]].float() for g in range(w.size(0))]).to(w.dtype)
+        return dx, dw, None
+
+
+def grouped_linear(x, w, m_offsets):
+    return _GroupedLinear.apply(x, w, m_offsets)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the layer
+# ---------------------------------------------------------------------------------------------------------
+class MoELayer(nn.Module):
+    """Top-k routed SwiGLU experts, block-partitioned over the ranks of ``buffer`` (expert e lives on rank e // (E/R))."""
+
+    def __init__(self, cfg: MoEConfig, buffer, device: Optional[torch.device] = None, seed: int = 0) -> None:
+        super().__init__()
+        self.cfg, self.buffer = cfg, buffer
+        R = buffer.group_size
+        assert cfg.num_experts % R == 0
+        self.num_local_experts = L = cfg.num_experts // R
+        dev = device if device is not None else (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.gate = nn.Parameter((torch.randn(cfg.num_experts, cfg.hidden, generator=g) * cfg.init_std).to(cfg.router_dtype).to(dev))
+        ge = torch.Generator(device="cpu").manual_seed(seed + 1 + buffer.rank)
+        self.w13 = nn.Parameter((torch.randn(L, 2 * cfg.intermediate, cfg.hidden, generator=ge) * cfg.init_std).to(torch.bfloat16).to(dev))
+        self.w2 = nn.Parameter((torch.randn(L, cfg.hidden, cfg.intermediate, generator=ge) * cfg.init_std).to(torch.bfloat16).to(dev))
+        self._fp8 = None
+
+    # -- routing ------------------------------------------------------------------------------------------
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        logits = x.to(self.gate.dtype) @ self.gate.t()
+        topk_logits, topk_idx = logits.topk(self.cfg.num_topk, dim=-1)
+        return topk_idx.to(torch.int64), torch.softmax(topk_logits.float(), dim=-1)
+
+    # -- BF16 path with autograd ----------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if topk_idx is None:
+            topk_idx, topk_weights = self.route(x)
+        routing = {}
+        recv_x, recv_w = _Dispatch.apply(x, topk_weights, topk_idx, self.buffer, self.cfg.num_experts, routing)
+        plan = build_expert_plan(routing["recv_topk_idx"], routing["counts"])
+        x_perm = permute(recv_x, plan)
+        h13 = grouped_linear(x_perm, self.w13, plan.m_offsets)
+        inter = self.cfg.intermediate
+        h = F.silu(h13[:, :inter].float()).mul(h13[:, inter:].float()).to(torch.bfloat16)
+        y_perm = grouped_linear(h, self.w2, plan.m_offsets)
+        out_buf = self._symmetric_like(recv_x)
+        y_recv = unpermute_weighted(y_perm, recv_w, plan, out_buf)
+        return _Combine.apply(y_recv, self.buffer, routing["handle"])
+
+    def _symmetric_like(self, recv_x: torch.Tensor) -> Optional[torch.Tensor]:
+        """Combine reads its input in place when it lives in the symmetric arena."""
+        if recv_x.is_cuda and getattr(self.buffer, "runtime", None) is not None:
+            return self.buffer.empty_symmetric(list(recv_x.shape), torch.bfloat16)
+        return None
+
+    # -- FP8 inference path -------------------------------------------------------------------------------------
+    def prepare_fp8(self) -> None:
+        """Quantise the expert weights to e4m3 with one fp32 scale per 128x128 block (done once)."""
+        def q(w):
+            G, N, K = w.shape
+            wb = w.detach().float().view(G, N // 128, 128, K // 128, 128)
+            s = (wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0).contiguous()
+            return (wb / s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous(), s
+        self._fp8 = (q(self.w13), q(self.w2))
+
+    @torch.no_grad()
+    def forward_fp8(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Forward only: FP8 on the wire and in both expert GEMMs, SwiGLU fused into the first GEMM, BF16 combine."""
+        from .. import _ext
+        C = _ext.load()
+        if self._fp8 is None:
+            self.prepare_fp8()
+        (w13, s13), (w2, s2) = self._fp8
+        if topk_idx is None:
+            topk_idx, topk_weights = self.route(x)
+        buf = self.buffer
+        per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(topk_idx, self.cfg.num_experts)
+        (rx, rs), recv_idx, recv_w, counts, handle, _ = buf.dispatch(
+            x, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert, topk_idx=topk_idx,
+            topk_weights=topk_weights, expert_alignment=EXPERT_ALIGNMENT, quantize_fp8=True)
+        plan = build_expert_plan(recv_idx, counts)
+        a = gather_rows(rx, plan.src_row)
+        a_s = gather_rows(rs, plan.src_row) if rs.size(1) % 4 == 0 else rs.index_select(0, plan.src_row.clamp(min=0).long())
+        h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, a_scales=a_s, b_scales=s13)
+        hq, hs = C.per_token_cast_to_fp8(h, False, False)
+        y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, a_scales=hs, b_scales=s2)
+        y_recv = unpermute_weighted(y_perm, recv_w, plan, buf.empty_symmetric([rx.size(0), self.cfg.hidden], torch.bfloat16))
+        out, _, _ = buf.combine(y_recv, handle)
+        return out
+
+
+def dense_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w13_all: torch.Tensor, w2_all: torch.Tensor) -> torch.Tensor:
+    """Single-process fp32 loop over all experts (w13_all [E, 2I, H], w2_all [E, H, I]); the oracle for the layer."""
+    out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+    inter = w2_all.size(2)
+    for e in range(w13_all.size(0)):
+        rows, ks = (topk_idx == e).nonzero(as_tuple=True)
+        if rows.numel() == 0:
+            continue
+        h = x[rows].float() @ w13_all[e].float().t()
+        h = F.silu(h[:, :inter]) * h[:, inter:]
+        y = h.to(torch.bfloat16).float() @ w2_all[e].float().t()
+        out.index_add_(0, rows, y * topk_weights[rows, ks].unsqueeze(1))
+    return out

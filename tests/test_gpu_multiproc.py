@@ -115,6 +115,28 @@ def _worker(rank, world, port, q):
                 buf.check_status()
                 want = x.float() * w.masked_fill(idx == -1, 0).sum(dim=1, keepdim=True)
                 assert oracle.calc_diff(want, o.float()) < (9e-4 if use_fp8 else 1e-5)
+        # ---- MoE layer forward + backward across ranks against the dense loop over all experts ----
+        from deepep_efa_b200.models.moe import MoEConfig, MoELayer, dense_reference
+        cfg = MoEConfig(hidden=512, intermediate=256, num_experts=E, num_topk=K, init_std=0.05)
+        layer = MoELayer(cfg, buf)
+        xm = make_tokens(T, 512, "cuda", seed=40 + rank).requires_grad_(True)
+        mi, mw = make_routing(T, E, K, "cuda", seed=40 + rank)
+        ym = layer(xm, mi, mw)
+        (ym.float() ** 2).mean().backward()
+        torch.cuda.synchronize()
+        buf.check_status()
+        w13_all = torch.cat([t.cuda() for t in gather(layer.w13.detach().cpu())]).float()
+        w2_all = torch.cat([t.cuda() for t in gather(layer.w2.detach().cpu())]).float()
+        xr = xm.detach().clone().requires_grad_(True)
+        ref = dense_reference(xr, mi, mw, w13_all, w2_all)
+        (ref ** 2).mean().backward()
+        rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-12)).item()
+        assert rel(ym, ref) < 3e-2, rel(ym, ref)
+        assert rel(xm.grad, xr.grad) < 6e-2, rel(xm.grad, xr.grad)
+        y8 = layer.forward_fp8(xm.detach(), mi, mw)
+        torch.cuda.synchronize()
+        buf.check_status()
+        assert rel(y8, ref.detach()) < 8e-2, rel(y8, ref.detach())
         buf.destroy()
         dist.destroy_process_group()
         q.put((rank, "ok"))

@@ -116,11 +116,16 @@ class MoELayer(nn.Module):
         assert cfg.num_experts % R == 0
         self.num_local_experts = L = cfg.num_experts // R
         dev = device if device is not None else (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
-        g = torch.Generator(device="cpu").manual_seed(seed)
-        self.gate = nn.Parameter((torch.randn(cfg.num_experts, cfg.hidden, generator=g) * cfg.init_std).to(cfg.router_dtype).to(dev))
-        ge = torch.Generator(device="cpu").manual_seed(seed + 1 + buffer.rank)
-        self.w13 = nn.Parameter((torch.randn(L, 2 * cfg.intermediate, cfg.hidden, generator=ge) * cfg.init_std).to(torch.bfloat16).to(dev))
-        self.w2 = nn.Parameter((torch.randn(L, cfg.hidden, cfg.intermediate, generator=ge) * cfg.init_std).to(torch.bfloat16).to(dev))
+        # weights are drawn on the target device (an expert-parallel shard of a large model does not fit a host pass)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.gate = nn.Parameter((torch.randn(cfg.num_experts, cfg.hidden, generator=g, device=dev) * cfg.init_std).to(cfg.router_dtype))
+        ge = torch.Generator(device=dev).manual_seed(seed + 1 + buffer.rank)
+        w13 = torch.empty(L, 2 * cfg.intermediate, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        w2 = torch.empty(L, cfg.hidden, cfg.intermediate, dtype=torch.bfloat16, device=dev)
+        for e in range(L):  # per expert, so the fp32 temporary stays small
+            w13[e] = (torch.randn(2 * cfg.intermediate, cfg.hidden, generator=ge, device=dev) * cfg.init_std).to(torch.bfloat16)
+            w2[e] = (torch.randn(cfg.hidden, cfg.intermediate, generator=ge, device=dev) * cfg.init_std).to(torch.bfloat16)
+        self.w13, self.w2 = nn.Parameter(w13), nn.Parameter(w2)
         self._fp8 = None
 
     # -- routing ------------------------------------------------------------------------------------------
@@ -156,9 +161,14 @@ class MoELayer(nn.Module):
         """Quantise the expert weights to e4m3 with one fp32 scale per 128x128 block (done once)."""
         def q(w):
             G, N, K = w.shape
-            wb = w.detach().float().view(G, N // 128, 128, K // 128, 128)
-            s = (wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0).contiguous()
-            return (wb / s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous(), s
+            out = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device=w.device)
+            scales = torch.empty(G, N // 128, K // 128, dtype=torch.float32, device=w.device)
+            for e in range(G):  # per expert: bounded fp32 temporaries
+                wb = w[e].detach().float().view(N // 128, 128, K // 128, 128)
+                s = (wb.abs().amax(dim=(1, 3)).clamp(min=1e-4) / 448.0)
+                out[e] = (wb / s.view(N // 128, 1, K // 128, 1)).view(N, K).to(torch.float8_e4m3fn)
+                scales[e] = s
+            return out, scales
         self._fp8 = (q(self.w13), q(self.w2))
 
     @torch.no_grad()

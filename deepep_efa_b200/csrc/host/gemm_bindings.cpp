@@ -116,6 +116,20 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     return c;
 }
 
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> build_plan(const torch::Tensor& topk_idx, const torch::Tensor& m_offsets, int64_t m_pad) {
+    DXG_CHECK(topk_idx.is_cuda() && topk_idx.dim() == 2 && topk_idx.is_contiguous() && topk_idx.scalar_type() == torch::kInt64, "topk_idx must be contiguous int64 [N,K] on the GPU");
+    DXG_CHECK(m_offsets.is_cuda() && m_offsets.scalar_type() == torch::kInt32 && m_offsets.is_contiguous() && m_offsets.numel() >= 2, "m_offsets must be int32 [L+1] on the GPU");
+    const int64_t N = topk_idx.size(0), K = topk_idx.size(1), L = m_offsets.numel() - 1;
+    c10::cuda::CUDAGuard guard(topk_idx.device());
+    auto i32 = topk_idx.options().dtype(torch::kInt32);
+    auto pos = torch::empty({N, K}, i32), src_row = torch::empty({m_pad}, i32), src_k = torch::empty({m_pad}, i32), counters = torch::empty({L}, i32);
+    const cudaError_t e = dx::launch_build_plan(topk_idx.data_ptr<int64_t>(), m_offsets.data_ptr<int>(), counters.data_ptr<int>(), pos.data_ptr<int>(),
+                                                src_row.data_ptr<int>(), src_k.data_ptr<int>(), (int)N, (int)K, (int)L, (int)m_pad,
+                                                at::cuda::getCurrentCUDAStream(topk_idx.device().index()).stream());
+    if (e != cudaSuccess) throw std::runtime_error(std::string("build_plan: ") + cudaGetErrorString(e));
+    return {pos, src_row, src_k};
+}
+
 // dst[m] = scale[m] * src[src_row[m]]; rows of any dtype whose byte size is a multiple of 16
 torch::Tensor gather_rows(const torch::Tensor& src, const torch::Tensor& src_row, c10::optional<torch::Tensor> scale,
                           c10::optional<torch::Tensor> out) {
@@ -168,6 +182,7 @@ void bind_gemm(py::module_& m) {
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
           py::arg("timeout_ms") = 2000.0);
+    m.def("build_plan", &build_plan);
     m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
     m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());
     m.def("gemm_error", &gemm_error);

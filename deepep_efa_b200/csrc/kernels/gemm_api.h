@@ -42,6 +42,11 @@ struct GroupedGemmArgs {
 // Returns cudaErrorInvalidValue for unsupported shapes (divisibility rules are in grouped_gemm.cu).
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& args, cudaStream_t stream);
 
+// Expert-major plan from local expert ids [N, K] (-1 = unselected) and 128-aligned group offsets [L+1]:
+// pos [N*K], src_row [m_pad] (-1 = padding), src_k [m_pad]; counters is an int[L] scratch.
+cudaError_t launch_build_plan(const int64_t* topk_idx, const int* m_offsets, int* counters, int* pos, int* src_row, int* src_k,
+                              int num_rows, int num_topk, int num_local_experts, int m_pad, cudaStream_t stream);
+
 // Row gathers between receive order and the expert-major, 128-row-aligned layout (permute.cu).
 //   dst[m] = scale[m] * src[src_row[m]]   (src_row[m] < 0 -> zero row; scale may be null; bf16 rows when scaled)
 cudaError_t launch_gather_rows(const void* src, void* dst, const int* src_row, const float* scale, int num_dst_rows, int row_bytes,

@@ -101,6 +101,54 @@ __global__ void __launch_bounds__(kPermThreads) gather_reduce_rows_kernel(const 
     }
 }
 
+// Expert-major slot assignment: selection (n, k) of local expert e gets row m_offsets[e] + (arrival order among the
+// selections of e). Which selection gets which row inside an expert does not matter (rows are independent in the
+// GEMM and the inverse map is built in the same pass), so slots are claimed with warp-aggregated atomics.
+__global__ void __launch_bounds__(256) build_plan_kernel(const int64_t* __restrict__ topk_idx, const int* __restrict__ m_offsets,
+                                                        int* __restrict__ counters, int* __restrict__ pos, int* __restrict__ src_row,
+                                                        int* __restrict__ src_k, int num_pairs, int num_topk, int num_local_experts) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    int e = -1;
+    if (i < num_pairs) {
+        const int64_t v = topk_idx[i];
+        if (v >= 0 && v < num_local_experts) e = (int)v;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    int p = -1;
+    if (e >= 0) {
+        const int leader = __ffs(peers) - 1;
+        int base = 0;
+        if (lane == leader) base = atomicAdd(&counters[e], __popc(peers));
+        base = __shfl_sync(peers, base, leader);
+        const int slot = base + __popc(peers & ((1u << lane) - 1));
+        const int row = m_offsets[e] + slot;
+        if (row < m_offsets[e + 1]) {  // cannot overflow when the offsets come from the dispatch counts
+            p = row;
+            src_row[row] = i / num_topk;
+            src_k[row] = i % num_topk;
+        }
+    }
+    if (i < num_pairs) pos[i] = p;
+}
+
+cudaError_t launch_build_plan(const int64_t* topk_idx, const int* m_offsets, int* counters, int* pos, int* src_row, int* src_k,
+                              int num_rows, int num_topk, int num_local_experts, int m_pad, cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(int) * num_local_experts, stream);
+    if (e != cudaSuccess) return e;
+    if (m_pad > 0) {
+        e = cudaMemsetAsync(src_row, 0xFF, sizeof(int) * (size_t)m_pad, stream);  // -1 = padding
+        if (e != cudaSuccess) return e;
+        e = cudaMemsetAsync(src_k, 0, sizeof(int) * (size_t)m_pad, stream);
+        if (e != cudaSuccess) return e;
+    }
+    const int pairs = num_rows * num_topk;
+    if (pairs <= 0) return cudaSuccess;
+    build_plan_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(topk_idx, m_offsets, counters, pos, src_row, src_k, pairs, num_topk,
+                                                              num_local_experts);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_gather_rows(const void* src, void* dst, const int* src_row, const float* scale, int num_dst_rows, int row_bytes,
                                cudaStream_t stream) {
     if (num_dst_rows <= 0) return cudaSuccess;

@@ -43,6 +43,9 @@ def build_expert_plan(recv_topk_idx: torch.Tensor, aligned_counts: List[int]) ->
         offs_host.append(offs_host[-1] + int(c))
     m_pad = offs_host[-1]
     m_offsets = torch.tensor(offs_host, dtype=torch.int32).to(dev, non_blocking=True)
+    if recv_topk_idx.is_cuda:
+        pos, src_row, src_k = _ext.load().build_plan(recv_topk_idx.contiguous(), m_offsets, m_pad)
+        return ExpertPlan(pos, src_row, src_k, m_offsets, m_pad)
     flat = recv_topk_idx.reshape(-1)
     valid = flat >= 0
     safe = flat.clamp(min=0)

@@ -23,16 +23,21 @@ def test_permute_kernels_match_indexing():
     xp = gather_rows(x, plan.src_row)
     o = plan.m_offsets.tolist()
     for e in range(L):
-        rows, _ = (idx == e).nonzero(as_tuple=True)
-        assert torch.equal(xp[o[e]:o[e] + rows.numel()], x[rows])
-        assert xp[o[e] + rows.numel():o[e + 1]].abs().sum().item() == 0
+        rows, ks = (idx == e).nonzero(as_tuple=True)
+        n = rows.numel()
+        seg_rows, seg_k = plan.src_row[o[e]:o[e] + n].long(), plan.src_k[o[e]:o[e] + n].long()
+        # the selections of an expert fill its segment in some order: same multiset of (row, k), payload follows src_row
+        assert torch.equal(torch.sort(seg_rows * K + seg_k).values, torch.sort(rows * K + ks).values)
+        assert torch.equal(xp[o[e]:o[e] + n], x[seg_rows])
+        assert (plan.src_row[o[e] + n:o[e + 1]] == -1).all() and xp[o[e] + n:o[e + 1]].abs().sum().item() == 0
+        assert torch.equal(plan.pos[seg_rows, seg_k].long(), torch.arange(o[e], o[e] + n, device="cuda"))
     w = torch.rand(N, K, device="cuda")
     y = gather_reduce_rows(xp, plan.pos, w)
     ref = x.float() * (w * (idx >= 0)).sum(1, keepdim=True)
     assert _rel(y, ref) < 1e-2
     # fp8 rows and fp32 scale rows go through the same byte-row gather
     q = x.to(torch.float8_e4m3fn)
-    assert torch.equal(gather_rows(q, plan.src_row).view(torch.uint8)[o[1]:o[1] + 3], q.view(torch.uint8)[(idx == 1).nonzero()[:3, 0]])
+    assert torch.equal(gather_rows(q, plan.src_row).view(torch.uint8)[o[1]:o[1] + 3], q.view(torch.uint8)[plan.src_row[o[1]:o[1] + 3].long()])
 
 
 def test_moe_layer_forward_backward_gpu():

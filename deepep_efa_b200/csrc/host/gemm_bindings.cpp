@@ -98,6 +98,10 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     p.c = c.data_ptr();
     p.m_offsets = m_offsets.data_ptr<int>();
     p.num_sms = num_sms > 0 ? num_sms : sm_count(device);
+    {
+        const char* o = std::getenv("DEEPEP_GEMM_ORDER");
+        p.tile_order = (o != nullptr && o[0] == '1') ? 1 : 0;
+    }
     p.error_flag = error_flag(device).data_ptr<int>();
     int khz = 0;
     cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device);

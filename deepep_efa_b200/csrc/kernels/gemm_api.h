@@ -35,6 +35,7 @@ struct GroupedGemmArgs {
     int n;                    // mode 0: rows of B per expert (2*I when swiglu); mode 1: N_out (rows of A)
     int k;                    // mode 0: reduction length; mode 1: K_out (rows of B)
     int num_sms;              // persistent grid size
+    int tile_order;           // mode 0: 0 = weight tile shared by consecutive CTAs, 1 = activation tile shared
     int* error_flag;          // device int, set non-zero when a bounded pipeline wait ran out
     long long timeout_cycles;
 };

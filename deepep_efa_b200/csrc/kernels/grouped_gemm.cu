@@ -5,7 +5,8 @@
 //   warp 0   : TMA producer   (one lane)  global -> smem ring, mbarrier complete_tx
 //   warp 1   : MMA issuer     (one lane)  tcgen05.mma, tcgen05.commit frees smem stages and publishes
 //                                         accumulator windows; also owns TMEM alloc / dealloc
-//   warps 2-5: epilogue       (128 thr)   tcgen05.ld -> registers -> (scale | SwiGLU) -> BF16 -> global
+//   warps 2.. : epilogue (4 warps for BF16, 8 for FP8)  tcgen05.ld -> registers -> (scale | SwiGLU) -> BF16 ->
+//                                         per-warp smem transpose -> coalesced global stores
 //
 // A tile is 128 rows x kBlockN columns; a K block is 128 bytes per row (64 BF16 or 128 e4m3), i.e. one
 // swizzle atom, consumed by four MMAs. Two accumulator windows in TMEM let the epilogue of window i
@@ -29,8 +30,6 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kKBlockBytes = 128;      // one 128B swizzle atom per row
-constexpr int kNumThreads = 192;
-constexpr int kNumEpilogueThreads = 128;
 constexpr int kATileBytes = kBlockM * kKBlockBytes;  // 16 KiB
 constexpr int kMaxGroups = 1024;
 
@@ -150,6 +149,38 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
+__device__ __forceinline__ int4 pack8_bf16(const float* o) {
+    int4 w;
+    __nv_bfloat162 t0 = __floats2bfloat162_rn(o[0], o[1]), t1 = __floats2bfloat162_rn(o[2], o[3]);
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(o[4], o[5]), t3 = __floats2bfloat162_rn(o[6], o[7]);
+    w.x = *reinterpret_cast<int*>(&t0);
+    w.y = *reinterpret_cast<int*>(&t1);
+    w.z = *reinterpret_cast<int*>(&t2);
+    w.w = *reinterpret_cast<int*>(&t3);
+    return w;
+}
+
+// Stores a 32-row x kCols BF16 block that a warp holds one row per lane. Writing it straight from registers would put
+// every lane on its own 32-byte sector (half filled); instead the block is transposed through a per-warp shared
+// buffer (XOR-swizzled 16-byte pieces) so that each store instruction covers whole rows: 128 contiguous bytes per row
+// for kCols = 64, 64 bytes for kCols = 32.
+template <int kCols>
+__device__ __forceinline__ void store_block_coalesced(int4* stage, const int4 (&regs)[kCols / 8], __nv_bfloat16* gbase, int ldc,
+                                                      int rows_valid, int lane) {
+    constexpr int P = kCols / 8;    // 16-byte pieces per row
+    constexpr int RPI = 32 / P;     // rows covered by one store instruction
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < P; ++j) stage[lane * P + (j ^ (lane & (P - 1)))] = regs[j];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+        const int row = i * RPI + lane / P, piece = lane % P;
+        const int4 v = stage[row * P + (piece ^ (row & (P - 1)))];
+        if (row < rows_valid) *reinterpret_cast<int4*>(gbase + (size_t)row * ldc + piece * 8) = v;
+    }
+}
+
 struct TileInfo {
     int a_row, a_k0, b_row, b_row2, b_k0, num_kb, c_row, c_col, group, nblock, nblock2;
 };
@@ -158,20 +189,27 @@ template <int kBlockN, bool kFp8, bool kSwiGLU>
 struct Cfg {
     static constexpr int kBTileBytes = kBlockN * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kStages = (kBlockN == 256) ? 4 : 6;
+    static constexpr int kStages = (kBlockN == 256) ? 4 : (kFp8 ? 5 : 6);
     static constexpr int kTmemCols = 2 * kBlockN;   // two accumulator windows
     static constexpr int kOutCols = kSwiGLU ? kBlockN / 2 : kBlockN;
-    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
+    // FP8 promotes every K block on the CUDA cores, so it gets two epilogue warps per TMEM lane quarter (each takes half
+    // of the columns); BF16 reads the accumulator once per tile and one warp per quarter is plenty.
+    static constexpr int kEpiWarps = kFp8 ? 8 : 4;
+    static constexpr int kThreads = 64 + 32 * kEpiWarps;
+    static constexpr int kOutStageBytes = 4096;    // per epilogue warp: 32 rows x 64 BF16
+    static constexpr size_t kSmemBytes =
+        (size_t)kStages * kStageBytes + (size_t)kEpiWarps * kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
 };
 
 template <int kBlockN, bool kFp8, bool kSwiGLU>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
     using C = Cfg<kBlockN, kFp8, kSwiGLU>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::kStages * C::kStageBytes);
+    uint8_t* out_stage_base = smem + (size_t)C::kStages * C::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage_base + (size_t)C::kEpiWarps * C::kOutStageBytes);
     uint64_t* full = bars;                       // [kStages]
     uint64_t* empty = bars + C::kStages;         // [kStages]
     uint64_t* tmem_full = bars + 2 * C::kStages; // [2]
@@ -192,7 +230,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmem_full[a], 1);
-            mbar_init(&tmem_empty[a], 4);
+            mbar_init(&tmem_empty[a], C::kEpiWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         tma_prefetch_desc(&map_a);
@@ -229,7 +267,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         ti.group = g;
         if (p.mode == 0) {
             const int tiles_m = (m1 - m0 + kBlockM - 1) / kBlockM;
-            const int nt = local / tiles_m, mt = local % tiles_m;  // consecutive tiles share the weight tile
+            const int tiles_n_ = p.n / kBlockN;
+            // order 0: consecutive tiles share the weight tile (n outer); order 1: they share the activation tile (m outer)
+            const int nt = p.tile_order == 0 ? local / tiles_m : local % tiles_n_;
+            const int mt = p.tile_order == 0 ? local % tiles_m : local / tiles_n_;
             ti.a_row = m0 + mt * kBlockM;
             ti.a_k0 = 0;
             ti.b_k0 = 0;
@@ -356,7 +397,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ================= epilogue =================
         const int q = warp & 3;                    // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;          // FP8 only: which half of the columns this warp promotes
         const int row_in_tile = q * 32 + lane;
+        int4* out_stage = reinterpret_cast<int4*>(out_stage_base + (size_t)(warp - 2) * C::kOutStageBytes);
         int g = 0, win = 0, win_phase = 0;
         TileInfo ti;
         bool ok = true;
@@ -368,15 +411,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int row = ti.c_row + row_in_tile;
             __nv_bfloat16* crow = cbase + (size_t)row * ldc + ti.c_col;
             if (ti.num_kb == 0) {
-                if (row < c_rows)
+                if (row < c_rows && half == 0)
                     for (int c = 0; c < C::kOutCols; c += 8) *reinterpret_cast<int4*>(crow + c) = make_int4(0, 0, 0, 0);
                 continue;
             }
             if constexpr (kFp8) {
-                // one window per K block, promoted into fp32 registers with the two scales
-                float acc[kBlockN];
+                // One window per K block, promoted into fp32 registers with the two scales. A warp owns two 32-column
+                // chunks: with SwiGLU a gate chunk and the matching up chunk, otherwise two neighbouring chunks.
+                constexpr int kLo0 = 0, kHalfCols = kBlockN / 2;
+                const int c_lo = kSwiGLU ? half * 32 : half * kHalfCols;
+                const int c_hi = kSwiGLU ? kHalfCols + half * 32 : half * kHalfCols + 32;
+                (void)kLo0;
+                float acc[64];
 #pragma unroll
-                for (int i = 0; i < kBlockN; ++i) acc[i] = 0.f;
+                for (int i = 0; i < 64; ++i) acc[i] = 0.f;
                 const int num_kscales = p.k / 128;
                 const int n_blocks = p.n / 128;
                 const float* sa_row = p.a_scales + (size_t)min(row, p.m_total - 1) * num_kscales;
@@ -384,45 +432,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float* sb1 = p.b_scales + ((size_t)ti.group * n_blocks + ti.nblock2) * num_kscales;
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
                     const float sa = __ldg(sa_row + kb);
-                    const float s0 = sa * __ldg(sb0 + kb), s1 = sa * __ldg(sb1 + kb);
+                    const float s_lo = sa * __ldg(sb0 + kb), s_hi = kSwiGLU ? sa * __ldg(sb1 + kb) : s_lo;
                     if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
-#pragma unroll
-                    for (int c = 0; c < kBlockN; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(taddr + c, v);
-                        tmem_ld_wait();
-                        const float s = (kSwiGLU && c >= kBlockN / 2) ? s1 : s0;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), s, acc[c + i]);
-                    }
+                    uint32_t v[32], u[32];
+                    tmem_ld32(taddr + c_lo, v);
+                    tmem_ld32(taddr + c_hi, u);
+                    tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&tmem_empty[win]);
+                    if (lane == 0) mbar_arrive(&tmem_empty[win]);  // the window is free as soon as it sits in registers
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        acc[i] = fmaf(__uint_as_float(v[i]), s_lo, acc[i]);
+                        acc[32 + i] = fmaf(__uint_as_float(u[i]), s_hi, acc[32 + i]);
+                    }
                     if (++win == 2) {
                         win = 0;
                         win_phase ^= 1;
                     }
                 }
                 if (!ok) break;
-                if (row < c_rows) {
+                {
+                    // rows of this warp: ti.c_row + q*32 .. +32; the block base is row 0 of the warp
+                    __nv_bfloat16* wbase = cbase + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
+                    const int rows_valid = min(32, c_rows - (ti.c_row + q * 32));
+                    if constexpr (kSwiGLU) {
+                        int4 regs[4];
 #pragma unroll
-                    for (int c = 0; c < C::kOutCols; c += 8) {
-                        float o[8];
+                        for (int c = 0; c < 32; c += 8) {
+                            float o[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) o[i] = kSwiGLU ? silu(acc[c + i]) * acc[kBlockN / 2 + c + i] : acc[c + i];
-                        int4 w;
-                        __nv_bfloat162 t0 = __floats2bfloat162_rn(o[0], o[1]), t1 = __floats2bfloat162_rn(o[2], o[3]);
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(o[4], o[5]), t3 = __floats2bfloat162_rn(o[6], o[7]);
-                        w.x = *reinterpret_cast<int*>(&t0);
-                        w.y = *reinterpret_cast<int*>(&t1);
-                        w.z = *reinterpret_cast<int*>(&t2);
-                        w.w = *reinterpret_cast<int*>(&t3);
-                        *reinterpret_cast<int4*>(crow + c) = w;
+                            for (int i = 0; i < 8; ++i) o[i] = silu(acc[c + i]) * acc[32 + c + i];
+                            regs[c / 8] = pack8_bf16(o);
+                        }
+                        store_block_coalesced<32>(out_stage, regs, wbase + half * 32, ldc, rows_valid, lane);
+                    } else {
+                        int4 regs[8];
+#pragma unroll
+                        for (int c = 0; c < 64; c += 8) regs[c / 8] = pack8_bf16(&acc[c]);
+                        store_block_coalesced<64>(out_stage, regs, wbase + half * kHalfCols, ldc, rows_valid, lane);
                     }
                 }
             } else {
@@ -432,34 +485,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
+                __nv_bfloat16* wbase = cbase + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
+                const int rows_valid = min(32, c_rows - (ti.c_row + q * 32));
+                if constexpr (kSwiGLU) {
 #pragma unroll 1
-                for (int c = 0; c < C::kOutCols; c += 32) {
-                    uint32_t v[32];
-                    float o[32];
-                    tmem_ld32(taddr + c, v);
-                    if constexpr (kSwiGLU) {
-                        uint32_t u[32];
+                    for (int c = 0; c < C::kOutCols; c += 32) {
+                        uint32_t v[32], u[32];
+                        tmem_ld32(taddr + c, v);
                         tmem_ld32(taddr + kBlockN / 2 + c, u);
                         tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = silu(__uint_as_float(v[i])) * __uint_as_float(u[i]);
-                    } else {
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]);
-                    }
-                    if (row < c_rows) {
+                        int4 regs[4];
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
-                            int4 w;
-                            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[i], o[i + 1]), t1 = __floats2bfloat162_rn(o[i + 2], o[i + 3]);
-                            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[i + 4], o[i + 5]), t3 = __floats2bfloat162_rn(o[i + 6], o[i + 7]);
-                            w.x = *reinterpret_cast<int*>(&t0);
-                            w.y = *reinterpret_cast<int*>(&t1);
-                            w.z = *reinterpret_cast<int*>(&t2);
-                            w.w = *reinterpret_cast<int*>(&t3);
-                            *reinterpret_cast<int4*>(crow + c + i) = w;
+                            float o[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) o[j] = silu(__uint_as_float(v[i + j])) * __uint_as_float(u[i + j]);
+                            regs[i / 8] = pack8_bf16(o);
                         }
+                        store_block_coalesced<32>(out_stage, regs, wbase + c, ldc, rows_valid, lane);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < C::kOutCols; c += 64) {
+                        uint32_t v[32], u[32];
+                        tmem_ld32(taddr + c, v);
+                        tmem_ld32(taddr + c + 32, u);
+                        tmem_ld_wait();
+                        int4 regs[8];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float o[8], o2[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                o[j] = __uint_as_float(v[i + j]);
+                                o2[j] = __uint_as_float(u[i + j]);
+                            }
+                            regs[i / 8] = pack8_bf16(o);
+                            regs[4 + i / 8] = pack8_bf16(o2);
+                        }
+                        store_block_coalesced<64>(out_stage, regs, wbase + c, ldc, rows_valid, lane);
                     }
                 }
                 tc_fence_before();
@@ -531,7 +595,7 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
     auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
     if (e != cudaSuccess) return e;
-    kernel<<<a.num_sms, kNumThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
+    kernel<<<a.num_sms, C::kThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
     return cudaGetLastError();
 }
 

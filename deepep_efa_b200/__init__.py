@@ -6,7 +6,7 @@ Public surface (same names as the reference's ``deep_ep`` package, deep_ep/__ini
 import torch
 
 from .utils.event import EventHandle, EventOverlap  # noqa: F401
-from .config import Config  # noqa: F401
+from .config import Config, LowLatencyLayout  # noqa: F401
 from .buffer import Buffer, EPTimeoutError, topk_idx_t  # noqa: F401
 
 __version__ = "0.1.0"

@@ -28,7 +28,9 @@ import torch.distributed as dist
 from . import _ext
 from .config import Config
 from .utils.event import EventHandle, EventOverlap
-from .utils.profiler import nvtx_range
+from .utils.logging import log as _log
+from .utils.profiler import PROFILE_ENABLED, PhaseProfiler, nvtx_range
+import logging as _logging
 
 topk_idx_t = torch.int64
 
@@ -186,6 +188,25 @@ class Buffer:
         from .config import get_low_latency_rdma_size_hint
         return get_low_latency_rdma_size_hint(num_max_dispatch_tokens_per_rank, hidden, num_ranks, num_experts)
 
+    # Accessors of the reference's runtime object (csrc/deep_ep.cpp:308-358), answered for one NVSwitch domain.
+    def is_available(self) -> bool:
+        return self._cpu is not None or (self.runtime is not None and self.runtime.is_available())
+
+    def get_num_rdma_ranks(self) -> int:
+        return 1
+
+    def get_rdma_rank(self) -> int:
+        return 0
+
+    def get_root_rdma_rank(self, global_: bool = True) -> int:
+        return 0
+
+    def get_local_device_id(self) -> int:
+        return self.device.index if self._cpu is None else -1
+
+    def get_local_ipc_handle(self) -> bytes:
+        return bytes(self.runtime.ipc_handle())
+
     def get_comm_stream(self) -> "torch.cuda.Stream":
         return self.comm_stream
 
@@ -245,6 +266,7 @@ class Buffer:
         """Collective reset after an error: zero the control block and all sequence state."""
         if self.runtime is None:
             return
+        _log(_logging.WARNING, self.rank, f"recovering buffer after: {self.runtime.status_string()}")
         torch.cuda.synchronize()
         if self.group is not None and self.group_size > 1:
             dist.barrier(self.group)
@@ -264,6 +286,7 @@ class Buffer:
         event)``; the second entry (tokens per RDMA rank) is always ``None`` inside one NVSwitch domain
         (deep_ep/buffer.py:422-448).
         """
+        topk_idx = _as_topk_idx(topk_idx)
         if self._cpu is not None:
             a, b, c = self._cpu.get_dispatch_layout(topk_idx, num_experts)
             return a, None, b, c, EventOverlap()
@@ -294,6 +317,7 @@ class Buffer:
         Rows of ``recv_x`` are ordered by source rank, then by token order at the source. The returned
         tensors live in this rank's symmetric arena; their memory returns to the arena when they die.
         """
+        topk_idx = _as_topk_idx(topk_idx)
         if self._cpu is not None:
             return self._cpu.dispatch(x, handle, num_tokens_per_rank, is_token_in_rank, num_tokens_per_expert, topk_idx,
                                       topk_weights, expert_alignment, num_worst_tokens)
@@ -385,10 +409,20 @@ class Buffer:
         second next low-latency dispatch. ``topk_weights`` is accepted for signature parity and unused.
         With ``return_recv_hook`` only the send half runs now and ``hook()`` launches the receive half.
         """
+        topk_idx = _as_topk_idx(topk_idx)
         if self._cpu is not None:
             return self._cpu.low_latency_dispatch(x, topk_idx, num_max_dispatch_tokens_per_rank, num_experts, use_fp8,
                                                   round_scale, use_ue8m0, cumulative_local_expert_recv_stats, return_recv_hook)
         assert not (async_finish and return_recv_hook)
+        if PROFILE_ENABLED:
+            prof = self.__dict__.setdefault("_ll_dispatch_profiler", PhaseProfiler("LL-DISPATCH", self.rank))
+            prof.mark("start")
+            res = _ll_dispatch_many([self], [(x, topk_idx, cumulative_local_expert_recv_stats, dispatch_wait_recv_cost_stats)],
+                                    num_max_dispatch_tokens_per_rank, num_experts, use_fp8, round_scale, use_ue8m0, async_finish,
+                                    return_recv_hook)[0]
+            prof.mark("kernel")
+            prof.finish_iter()
+            return res
         return _ll_dispatch_many([self], [(x, topk_idx, cumulative_local_expert_recv_stats, dispatch_wait_recv_cost_stats)],
                                  num_max_dispatch_tokens_per_rank, num_experts, use_fp8, round_scale, use_ue8m0, async_finish,
                                  return_recv_hook)[0]
@@ -403,9 +437,18 @@ class Buffer:
         input is read from the buffer returned by :meth:`get_next_low_latency_combine_buffer` and ``x`` is ignored.
         ``use_logfmt`` (a 10-bit wire format of upstream DeepEP) is accepted and ignored: rows travel as bf16.
         """
+        topk_idx = _as_topk_idx(topk_idx)
         if self._cpu is not None:
             return self._cpu.low_latency_combine(x, topk_idx, topk_weights, handle, out, return_recv_hook)
         assert not (async_finish and return_recv_hook)
+        if PROFILE_ENABLED:
+            prof = self.__dict__.setdefault("_ll_combine_profiler", PhaseProfiler("LL-COMBINE", self.rank))
+            prof.mark("start")
+            res = _ll_combine_many([self], [(x, topk_idx, topk_weights, handle, out, combine_wait_recv_cost_stats)], zero_copy,
+                                   async_finish, return_recv_hook)[0]
+            prof.mark("kernel")
+            prof.finish_iter()
+            return res
         return _ll_combine_many([self], [(x, topk_idx, topk_weights, handle, out, combine_wait_recv_cost_stats)], zero_copy,
                                 async_finish, return_recv_hook)[0]
 
@@ -444,6 +487,14 @@ class Buffer:
 # ================================================================================================
 # helpers shared by the single-rank API above and the single-GPU multi-rank emulation
 # ================================================================================================
+def _as_topk_idx(topk_idx):
+    """The kernels take int64 expert ids (``topk_idx_t``); int32 ids (the reference's TOPK_IDX_BITS=32 build,
+    csrc/kernels/configs.cuh:66-72) are widened."""
+    if topk_idx is not None and topk_idx.dtype != torch.int64:
+        return topk_idx.to(torch.int64)
+    return topk_idx
+
+
 class _DispatchReq:
     __slots__ = ("x", "handle", "num_tokens_per_rank", "is_token_in_rank", "num_tokens_per_expert", "topk_idx",
                  "topk_weights", "expert_alignment", "num_worst_tokens", "quantize_fp8", "round_scale")

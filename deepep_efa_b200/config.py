@@ -11,6 +11,7 @@ from . import _ext
 
 _C = _ext.load()
 Config = _C.Config
+LowLatencyLayout = _C.LowLatencyLayout
 
 # num_ranks -> (num_sms, nvl_send, nvl_recv, rdma_send, rdma_recv)
 DISPATCH_CONFIGS = {

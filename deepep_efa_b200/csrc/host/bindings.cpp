@@ -571,6 +571,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("get_low_latency_rdma_size_hint", &dxh::get_low_latency_rdma_size_hint, py::arg("num_max_dispatch_tokens_per_rank"),
           py::arg("hidden"), py::arg("num_ranks"), py::arg("num_experts"));
     m.attr("CONTROL_BYTES") = (int64_t)dxh::kControlBytes;
+    py::class_<dxh::LowLatencyLayout>(m, "LowLatencyLayout")
+        .def(py::init<uint64_t, int, int, int, int>(), py::arg("base"), py::arg("num_max_dispatch_tokens_per_rank"), py::arg("hidden"),
+             py::arg("num_ranks"), py::arg("num_experts"))
+        .def_readonly("total_bytes", &dxh::LowLatencyLayout::total_bytes)
+        .def_property_readonly("counts_off", [](const dxh::LowLatencyLayout& l) { return std::make_pair(l.counts_off[0], l.counts_off[1]); })
+        .def_property_readonly("recv_x_off", [](const dxh::LowLatencyLayout& l) { return std::make_pair(l.recv_x_off[0], l.recv_x_off[1]); })
+        .def_property_readonly("recv_scales_off", [](const dxh::LowLatencyLayout& l) { return std::make_pair(l.recv_scales_off[0], l.recv_scales_off[1]); })
+        .def_property_readonly("recv_src_info_off", [](const dxh::LowLatencyLayout& l) { return std::make_pair(l.recv_src_info_off[0], l.recv_src_info_off[1]); })
+        .def_property_readonly("combine_stage_off", [](const dxh::LowLatencyLayout& l) { return std::make_pair(l.combine_stage_off[0], l.combine_stage_off[1]); })
+        .def_property_readonly("combine_src_off", [](const dxh::LowLatencyLayout& l) { return std::make_pair(l.combine_src_off[0], l.combine_src_off[1]); });
 
     py::class_<dxh::Arena>(m, "Arena")
         .def(py::init<uint64_t, uint64_t, uint64_t>(), py::arg("base"), py::arg("size"), py::arg("align") = 1024)

@@ -66,3 +66,14 @@ def test_arena_random_stress():
     for off in list(live):
         a.free(off)
     assert a.in_use == 0 and a.num_free_blocks == 1
+
+
+def test_low_latency_layout_class():
+    import deepep_efa_b200 as ep
+    lay = ep.LowLatencyLayout(C.CONTROL_BYTES, 128, 7168, 8, 256)
+    offs = [lay.counts_off, lay.recv_x_off, lay.recv_scales_off, lay.recv_src_info_off, lay.combine_stage_off, lay.combine_src_off]
+    flat = sorted(o for pair in offs for o in pair)
+    assert flat[0] == C.CONTROL_BYTES and all(b > a for a, b in zip(flat, flat[1:])) and all(o % 1024 == 0 for o in flat)
+    assert lay.total_bytes + C.CONTROL_BYTES <= ep.Buffer.get_low_latency_rdma_size_hint(128, 7168, 8, 256) + 128
+    # recv_x is sized for BF16 dispatch: L * N * hidden * 2 bytes per parity
+    assert lay.recv_scales_off[0] - lay.recv_x_off[0] >= 32 * 1024 * 7168 * 2

@@ -143,22 +143,31 @@ def _bench_normal(deep_ep, buf, rank, world, flush, steps, warmup, B):
     deep_ep.Buffer.set_num_sms(24)
     per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(topk_idx, E)
     best = {}
-    handle_ref = None
+    # one fresh dispatch gives the handle; the timed calls reuse it, exactly as the reference's own tuning loop does
+    # (tests/test_intranode.py:200-214: tune_args = {'x': current_x, 'handle': handle, 'config': config})
+    first = buf.dispatch(x_e4m3, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert,
+                         topk_idx=topk_idx, topk_weights=topk_w)
+    n_recv = first[0][0].size(0)
+    handle_ref = first[4]
     for chunk in (8, 16, 24, 32):
         cfg = deep_ep.Config(24, chunk, 256)
-        state = {}
 
         def do_dispatch():
-            state["r"] = buf.dispatch(x_e4m3, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert,
-                                      topk_idx=topk_idx, topk_weights=topk_w, config=cfg)
+            buf.dispatch(x_e4m3, handle=handle_ref, config=cfg)
         for _ in range(warmup):
             do_dispatch()
         ms = B.max_over_ranks(B.timed_loop(do_dispatch, steps, flush))
-        n_recv = state["r"][0][0].size(0)
-        handle_ref = state["r"][4]
         gbps = n_recv * H * 2 * (1 + 4 / 128) / 2 / 1e9 / (ms / 1e3)
-        if "dispatch_fp8" not in best or gbps > best["dispatch_fp8"]["GBps"]:
-            best["dispatch_fp8"] = {"ms": round(ms, 4), "GBps": round(gbps, 1), "chunk": chunk}
+        if "dispatch_fp8_cached" not in best or gbps > best["dispatch_fp8_cached"]["GBps"]:
+            best["dispatch_fp8_cached"] = {"ms": round(ms, 4), "GBps": round(gbps, 1), "chunk": chunk}
+
+    def do_fresh():
+        buf.dispatch(x_e4m3, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert,
+                     topk_idx=topk_idx, topk_weights=topk_w, config=deep_ep.Config(24, best["dispatch_fp8_cached"]["chunk"], 256))
+    for _ in range(warmup):
+        do_fresh()
+    ms = B.max_over_ranks(B.timed_loop(do_fresh, steps, flush))
+    best["dispatch_fp8"] = {"ms": round(ms, 4), "GBps": round(n_recv * H * 2 * (1 + 4 / 128) / 2 / 1e9 / (ms / 1e3), 1)}
     y = torch.randn(n_recv, H, device="cuda").to(torch.bfloat16)
     for chunk in (2, 4, 8, 16):
         cfg = deep_ep.Config(24, chunk, 256)

@@ -190,7 +190,10 @@ struct Cfg {
     static constexpr int kBTileBytes = kBlockN * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kStages = (kBlockN == 256) ? 4 : (kFp8 ? 5 : 6);
-    static constexpr int kTmemCols = 2 * kBlockN;   // two accumulator windows
+    // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
+    // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
+    static constexpr int kWindows = kFp8 ? 4 : 2;
+    static constexpr int kTmemCols = kWindows * kBlockN;
     static constexpr int kOutCols = kSwiGLU ? kBlockN / 2 : kBlockN;
     // FP8 promotes every K block on the CUDA cores, so it gets two epilogue warps per TMEM lane quarter (each takes half
     // of the columns); BF16 reads the accumulator once per tile and one warp per quarter is plenty.
@@ -212,8 +215,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage_base + (size_t)C::kEpiWarps * C::kOutStageBytes);
     uint64_t* full = bars;                       // [kStages]
     uint64_t* empty = bars + C::kStages;         // [kStages]
-    uint64_t* tmem_full = bars + 2 * C::kStages; // [2]
-    uint64_t* tmem_empty = tmem_full + 2;        // [2]
+    uint64_t* tmem_full = bars + 2 * C::kStages; // [kWindows]
+    uint64_t* tmem_empty = tmem_full + C::kWindows;  // [kWindows]
     int* tile_start = reinterpret_cast<int*>(bars + 32);  // [G+1] first tile index of every group
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -228,7 +231,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < C::kWindows; ++a) {
             mbar_init(&tmem_full[a], 1);
             mbar_init(&tmem_empty[a], C::kEpiWarps);
         }
@@ -382,7 +385,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const bool window_done = kFp8 ? true : (kb == ti.num_kb - 1);
                     if (window_done) {
                         umma_commit(&tmem_full[win]);
-                        if (++win == 2) {
+                        if (++win == C::kWindows) {
                             win = 0;
                             win_phase ^= 1;
                         }
@@ -451,7 +454,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         acc[i] = fmaf(__uint_as_float(v[i]), s_lo, acc[i]);
                         acc[32 + i] = fmaf(__uint_as_float(u[i]), s_hi, acc[32 + i]);
                     }
-                    if (++win == 2) {
+                    if (++win == C::kWindows) {
                         win = 0;
                         win_phase ^= 1;
                     }
@@ -529,7 +532,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tmem_empty[win]);
-                if (++win == 2) {
+                if (++win == C::kWindows) {
                     win = 0;
                     win_phase ^= 1;
                 }

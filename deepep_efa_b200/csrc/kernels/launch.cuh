@@ -18,7 +18,7 @@ struct ArgPack {
 
 template <typename Args, int V>
 cudaError_t launch_ranked(void (*kernel)(const ArgPack<Args, V>), const Args* args, int num_virtual, int ctas_per_rank,
-                          int threads, size_t smem, cudaStream_t stream) {
+                          int threads, size_t smem, cudaStream_t stream, bool programmatic = false) {
     ArgPack<Args, V> pack;
     for (int i = 0; i < num_virtual; ++i) pack.a[i] = args[i];
     for (int i = num_virtual; i < V; ++i) pack.a[i] = args[0];
@@ -32,8 +32,15 @@ cudaError_t launch_ranked(void (*kernel)(const ArgPack<Args, V>), const Args* ar
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = num_virtual > 1 ? 1 : 0;
+    if (num_virtual > 1) {
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+    } else {
+        // Programmatic dependent launch: the launch work of this kernel overlaps the tail of the previous kernel in
+        // the stream; the kernel itself calls griddepcontrol.wait before it touches anything the predecessor wrote.
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = programmatic ? 1 : 0;
+    }
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, pack);
@@ -42,6 +49,12 @@ cudaError_t launch_ranked(void (*kernel)(const ArgPack<Args, V>), const Args* ar
 // Picks the 1-rank or the 8-rank instantiation.
 #define DX_LAUNCH_RANKED(KERNEL, ARGS_T, args, nv, ctas, threads, smem, stream)                                 \
     ((nv) == 1 ? ::dx::launch_ranked<ARGS_T, 1>(KERNEL<1>, args, 1, ctas, threads, smem, stream)                \
+               : ::dx::launch_ranked<ARGS_T, ::dx::kMaxVirtualRanks>(KERNEL<::dx::kMaxVirtualRanks>, args, nv, \
+                                                                    ctas, threads, smem, stream))
+
+// Same, with programmatic dependent launch enabled for the single-rank instantiation.
+#define DX_LAUNCH_RANKED_PDL(KERNEL, ARGS_T, args, nv, ctas, threads, smem, stream)                             \
+    ((nv) == 1 ? ::dx::launch_ranked<ARGS_T, 1>(KERNEL<1>, args, 1, ctas, threads, smem, stream, true)          \
                : ::dx::launch_ranked<ARGS_T, ::dx::kMaxVirtualRanks>(KERNEL<::dx::kMaxVirtualRanks>, args, nv, \
                                                                     ctas, threads, smem, stream))
 

@@ -91,6 +91,8 @@ __device__ __forceinline__ QuantChunk quantize_chunk(const char* row, int ch, bo
 // =============================================================================================
 template <int V>
 __global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid_constant__ ArgPack<LLDispatchArgs, V> pack) {
+    pdl_wait_predecessor();
+    pdl_release_successor();
     const LLDispatchArgs& a = pack.a[blockIdx.y];
     const RankCtx& c = a.ctx;
     const int R = c.num_ranks, me = c.rank, T = a.num_tokens, K = a.num_topk, E = a.num_experts;
@@ -309,7 +311,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid
 
 cudaError_t launch_ll_dispatch(const LLDispatchArgs* a, int nv, cudaStream_t stream) {
     const size_t smem = ((size_t)a[0].num_tokens * a[0].num_topk + a[0].num_experts) * sizeof(int);
-    return DX_LAUNCH_RANKED(ll_dispatch_kernel, LLDispatchArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
+    return DX_LAUNCH_RANKED_PDL(ll_dispatch_kernel, LLDispatchArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
 }
 
 // =============================================================================================
@@ -317,6 +319,8 @@ cudaError_t launch_ll_dispatch(const LLDispatchArgs* a, int nv, cudaStream_t str
 // =============================================================================================
 template <int V>
 __global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_constant__ ArgPack<LLCombineArgs, V> pack) {
+    pdl_wait_predecessor();
+    pdl_release_successor();
     const LLCombineArgs& a = pack.a[blockIdx.y];
     const RankCtx& c = a.ctx;
     const int R = c.num_ranks, me = c.rank, T = a.num_tokens, K = a.num_topk, E = a.num_experts;
@@ -514,7 +518,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_
 
 cudaError_t launch_ll_combine(const LLCombineArgs* a, int nv, cudaStream_t stream) {
     const size_t smem = ((size_t)a[0].num_experts / a[0].ctx.num_ranks + 1) * sizeof(int);
-    return DX_LAUNCH_RANKED(ll_combine_kernel, LLCombineArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
+    return DX_LAUNCH_RANKED_PDL(ll_combine_kernel, LLCombineArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
 }
 
 }  // namespace dx

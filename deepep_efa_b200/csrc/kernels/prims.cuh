@@ -195,6 +195,11 @@ __device__ __forceinline__ void commit_seq(const RankCtx& c, int fam, uint64_t s
     *reinterpret_cast<volatile uint64_t*>(c.seq + fam) = seq;
 }
 
+// Programmatic dependent launch: wait until the predecessor kernel in the stream has completed (and its memory is
+// visible), and allow the successor's launch to be prepared. Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_wait_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_successor() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Phase time stamp (nanoseconds of the GPU's global timer) for the tracing facility; free when tracing is off.
 __device__ __forceinline__ void trace_stamp(const RankCtx& c, int fam, int slot, int idx) {
     if (c.trace != nullptr && threadIdx.x == 0) {

@@ -556,6 +556,30 @@ class _CommScope:
         return False
 
 
+_DEBUG_CHECKS = os.environ.get("DEEPEP_DEBUG_CHECKS", "0") == "1"
+
+
+def validate_handle(handle: Tuple, rank: int, num_ranks: int) -> None:
+    """Debug aid (``DEEPEP_DEBUG_CHECKS=1`` runs it before every cached dispatch and every combine; it synchronises):
+    checks that a normal-mode handle is self-consistent, so that a corrupted or foreign handle is reported on the host
+    instead of making a kernel write outside a peer's tensors. compute-sanitizer is not available on every
+    machine; these checks cover the addresses the kernels derive from the handle."""
+    rpm, cpm, rcpm, recv_src_idx, in_rank, send_head = handle
+    assert rpm.shape == (num_ranks, num_ranks) and send_head.shape[1] == num_ranks and in_rank.shape == send_head.shape
+    r = rpm.cpu().long()
+    assert (r[1:] >= r[:-1]).all() and (r >= 0).all(), "rank_prefix_matrix must be a non-decreasing inclusive prefix"
+    assert int(r[-1, rank]) == recv_src_idx.numel(), "handle does not belong to this rank (receive count mismatch)"
+    sh = send_head.cpu().long()
+    sent = r[rank] - (r[rank - 1] if rank > 0 else 0)
+    for d in range(num_ranks):
+        col = sh[:, d]
+        pos = col[col >= 0]
+        assert pos.numel() == int(sent[d]), f"send_head column {d} disagrees with the prefix matrix"
+        if pos.numel():
+            assert torch.equal(pos, torch.arange(pos.numel())), f"send_head column {d} is not a dense 0..n-1 sequence"
+    assert torch.equal(in_rank.cpu(), sh >= 0), "is_token_in_rank disagrees with send_head"
+
+
 def _clamp_sms(num_sms: int, num_virtual: int) -> int:
     # all CTAs of all emulated ranks must be co-resident (cooperative launch)
     return num_sms if num_virtual == 1 else max(1, min(num_sms, _NUM_SM_B200 // num_virtual - 1))
@@ -584,6 +608,8 @@ def _dispatch_many(bufs: List[Buffer], reqs: List[_DispatchReq], config: Config,
             for q in reqs:
                 assert q.topk_idx is None and q.topk_weights is None, "cached dispatch carries no top-k data"
                 rpm, cpm, rcpm, recv_src_idx, itir, send_head = q.handle
+                if _DEBUG_CHECKS:
+                    validate_handle(q.handle, bufs[len(metas)].rank, R)
                 metas.append((rpm, cpm, rcpm, send_head, itir, recv_src_idx.size(0), []))
         else:
             for q in reqs:
@@ -646,6 +672,8 @@ def _combine_many(bufs: List[Buffer], calls, config: Config, previous_event, asy
     with _CommScope(bufs[0], previous_event, async_finish, allocate_on_comm_stream, inputs) as scope, nvtx_range("ep.combine"):
         for b, (x, handle, w, bias) in zip(bufs, calls):
             rpm, _, _, src_idx, _, send_head = handle
+            if _DEBUG_CHECKS:
+                validate_handle(handle, b.rank, b.group_size)
             rt = b.runtime
             assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.size(0) == src_idx.size(0)
             if rt.symmetric_offset(x) < 0:

@@ -206,3 +206,26 @@ def test_arena_memory_returns():
         assert vc.buffers[0].runtime.arena_in_use() <= vc.buffers[0].runtime.arena_capacity()
     finally:
         vc.destroy()
+
+
+def test_handle_validation_catches_foreign_and_corrupt_handles():
+    from deepep_efa_b200.buffer import validate_handle
+    R = 4
+    vc = _cluster(R)
+    try:
+        T, H, E, K = 64, 512, 16, 4
+        xs, idxs, ws = _inputs(R, T, H, E, K, seed=2)
+        lay = vc.get_dispatch_layout(idxs, E)
+        res = vc.dispatch(xs, layouts=lay, topk_idxs=idxs, topk_weights=ws)
+        for r in range(R):
+            validate_handle(res[r][4], r, R)
+        with pytest.raises(AssertionError):
+            validate_handle(res[1][4], 2, R)  # another rank's handle
+        h = list(res[0][4])
+        bad = h[5].clone()
+        bad[bad >= 0] += 1  # positions no longer start at zero
+        h[5] = bad
+        with pytest.raises(AssertionError):
+            validate_handle(tuple(h), 0, R)
+    finally:
+        vc.destroy()

@@ -83,12 +83,14 @@ def main(args) -> None:
         buf.low_latency_combine(sim, topk_idx, topk_w, handle)
 
     try:
+        sampler = B.ClockSampler() if rank == 0 else None
+        if sampler is not None:
+            sampler.start()
         for _ in range(warmup):
             ll_step()
-        sampler = B.ClockSampler(B.physical_gpu_index(local_rank))
-        sampler.start()
         ll_us = B.max_over_ranks(B.timed_loop(ll_step, steps, flush) * 1e3)
-        clocks = sampler.stop()
+        clocks = sampler.stop({B.physical_gpu_index(r) for r in range(world)}) if sampler is not None else \
+            {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         result.update(value=round(ll_us, 3), ms_per_step=round(ll_us / 1e3, 6), vs_baseline=round(ll_us / B.PUBLISHED_LL_US, 5),
                       clocks={"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                               "samples": clocks["samples"]})

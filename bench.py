@@ -42,13 +42,14 @@ PUBLISHED_LL_US = 1145.0  # reference README.md:83, EP16 on 2 nodes (no single-n
 # clocks
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons with one nvidia-smi process (all GPUs, time-stamped lines) while a region
+    runs; ``stop(gpus)`` keeps the lines of the given physical GPU indices."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int, period_ms: int = 20):
-        self.gpu_index, self.period_ms = gpu_index, period_ms
+    def __init__(self, period_ms: int = 100):
+        self.period_ms = period_ms
         self.proc, self.path = None, None
 
     def start(self):
@@ -56,13 +57,12 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
-                                         stdout=self.out, stderr=subprocess.DEVNULL)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms",
+                                          str(self.period_ms)], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, gpus):
         res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return res
@@ -79,7 +79,9 @@ class ClockSampler:
                 if len(p) < 9:
                     continue
                 try:
-                    sm.append(float(p[1])), smax.append(float(p[2]))
+                    if int(p[1]) not in gpus:
+                        continue
+                    sm.append(float(p[2])), smax.append(float(p[3]))
                 except ValueError:
                     continue
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
@@ -186,12 +188,14 @@ def run_ours(args):
     diff = oracle.calc_diff(x.float() * topk_w.sum(1, keepdim=True), chk.float())
     assert diff < 9e-4, f"low-latency round trip is wrong: diff={diff}"
 
+    # one sampler (rank 0) for all GPUs of the job; it runs from the warm-up through both timed regions (device-timed and
+    # end-to-end), which execute the same workload back to back
+    sampler = ClockSampler() if rank == 0 else None
+    if sampler is not None:
+        sampler.start()
     for _ in range(warmup):
         ll_step()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
     ll_ms = timed_loop(ll_step, steps, flush)
-    clocks = sampler.stop()
     buf.check_status(sync=True)
     ll_us = max_over_ranks(ll_ms * 1e3)
 
@@ -239,6 +243,9 @@ def run_ours(args):
     h2d = x_p.numel() * 2 + idx_p.numel() * 8 + w_p.numel() * 4
     d2h = out_p.numel() * 2
     buf.check_status(sync=True)
+    clocks = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    if sampler is not None:
+        clocks = sampler.stop({physical_gpu_index(r) for r in range(world)})
 
     # ---------------- masked-slot sweep (2 % / 5 % of the top-k slots are -1) ----------------
     masked = {}

@@ -386,14 +386,19 @@ void timeout_probe(Runtime* rt) {
 // ---------------------------------------------------------------------------------------------
 // FP8 cast
 // ---------------------------------------------------------------------------------------------
-std::tuple<torch::Tensor, torch::Tensor> per_token_cast_to_fp8(const torch::Tensor& x, bool round_scale, bool use_ue8m0) {
+std::tuple<torch::Tensor, torch::Tensor> per_token_cast_to_fp8(const torch::Tensor& x, bool round_scale, bool use_ue8m0,
+                                                               c10::optional<torch::Tensor> group_counts, int rows_per_group,
+                                                               c10::optional<torch::Tensor> out_q, c10::optional<torch::Tensor> out_s) {
     DX_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "x must be contiguous bf16 [M,hidden] on the GPU");
     const int M = (int)x.size(0), H = (int)x.size(1);
     DX_CHECK(H % 128 == 0 && (!use_ue8m0 || H % 512 == 0), "hidden must be a multiple of 128 (512 for UE8M0 scales)");
     c10::cuda::CUDAGuard guard(x.device());
-    auto out = torch::empty({M, H}, x.options().dtype(torch::kFloat8_e4m3fn));
-    torch::Tensor scales = use_ue8m0 ? torch::empty({M, H / 512}, x.options().dtype(torch::kInt32))
-                                     : torch::empty({M, H / 128}, x.options().dtype(torch::kFloat32));
+    auto out = out_q.has_value() ? *out_q : torch::empty({M, H}, x.options().dtype(torch::kFloat8_e4m3fn));
+    torch::Tensor scales = out_s.has_value() ? *out_s
+                           : (use_ue8m0 ? torch::empty({M, H / 512}, x.options().dtype(torch::kInt32))
+                                        : torch::empty({M, H / 128}, x.options().dtype(torch::kFloat32)));
+    DX_CHECK(out.is_contiguous() && out.numel() == (int64_t)M * H && out.element_size() == 1, "out_q must be a contiguous 1-byte [M,hidden] tensor");
+    DX_CHECK(scales.is_contiguous() && scales.numel() == (int64_t)M * (use_ue8m0 ? H / 512 : H / 128) && scales.element_size() == 4, "out_s has the wrong shape");
     dx::Fp8CastArgs a;
     a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
     a.out = reinterpret_cast<uint8_t*>(out.data_ptr());
@@ -403,6 +408,14 @@ std::tuple<torch::Tensor, torch::Tensor> per_token_cast_to_fp8(const torch::Tens
     a.hidden = H;
     a.round_scale = round_scale ? 1 : 0;
     a.ue8m0 = use_ue8m0 ? 1 : 0;
+    a.group_counts = nullptr;
+    a.rows_per_group = 1;
+    if (group_counts.has_value()) {
+        DX_CHECK(group_counts->is_cuda() && group_counts->scalar_type() == torch::kInt32 && group_counts->is_contiguous() && rows_per_group > 0 &&
+                     group_counts->numel() * (int64_t)rows_per_group == M, "group_counts must be int32 [M / rows_per_group]");
+        a.group_counts = group_counts->data_ptr<int>();
+        a.rows_per_group = rows_per_group;
+    }
     check_launch(dx::launch_fp8_cast(a, c10::cuda::getCurrentCUDAStream(x.device().index()).stream()), "per_token_cast_to_fp8");
     return {out, scales};
 }
@@ -634,7 +647,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("combine", &combine);
     m.def("barrier", &barrier);
     m.def("timeout_probe", &timeout_probe);
-    m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false, py::arg("use_ue8m0") = false);
+    m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false, py::arg("use_ue8m0") = false,
+          py::arg("group_counts") = py::none(), py::arg("rows_per_group") = 1, py::arg("out_q") = py::none(), py::arg("out_s") = py::none());
     m.def("ll_dispatch", &ll_dispatch);
     m.def("ll_combine", &ll_combine);
     m.def("ll_layout", &ll_layout);

@@ -45,7 +45,7 @@ int sm_count(int device) {
 // mode 1: a [N_out, M], b [K_out, M], m_offsets [G+1] -> c [G, N_out, K_out]
 torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& m_offsets, int mode, bool swiglu,
                            c10::optional<torch::Tensor> a_scales, c10::optional<torch::Tensor> b_scales,
-                           c10::optional<torch::Tensor> out, int num_sms, double timeout_ms) {
+                           c10::optional<torch::Tensor> out, int num_sms, double timeout_ms, c10::optional<torch::Tensor> m_ends) {
     DXG_CHECK(a.is_cuda() && b.is_cuda() && m_offsets.is_cuda(), "operands must be CUDA tensors");
     DXG_CHECK(a.is_contiguous() && b.is_contiguous() && m_offsets.is_contiguous(), "operands must be contiguous");
     DXG_CHECK(m_offsets.scalar_type() == torch::kInt32 && m_offsets.dim() == 1 && m_offsets.numel() >= 2, "m_offsets must be int32 [G+1]");
@@ -97,6 +97,11 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     p.b = b.data_ptr();
     p.c = c.data_ptr();
     p.m_offsets = m_offsets.data_ptr<int>();
+    p.m_ends = nullptr;
+    if (m_ends.has_value()) {
+        DXG_CHECK(mode == 0 && m_ends->is_cuda() && m_ends->scalar_type() == torch::kInt32 && m_ends->is_contiguous() && m_ends->numel() == G, "m_ends must be int32 [G] on the GPU (M-grouped mode only)");
+        p.m_ends = m_ends->data_ptr<int>();
+    }
     p.num_sms = num_sms > 0 ? num_sms : sm_count(device);
     {
         const char* o = std::getenv("DEEPEP_GEMM_ORDER");
@@ -110,8 +115,8 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     if (e == cudaErrorInvalidValue) {
         cudaGetLastError();
         throw std::invalid_argument(
-            "deepep_efa_b200.grouped_gemm: unsupported shape (need K % 64 == 0 for bf16 / % 128 for fp8, N % 128 == 0, group "
-            "boundaries on multiples of 128)");
+            "deepep_efa_b200.grouped_gemm: unsupported shape (need K % 64 == 0 for bf16 / % 128 for fp8, N % 128 == 0; the "
+            "K-grouped mode needs group boundaries on multiples of 128)");
     }
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -185,7 +190,7 @@ void gemm_clear_error(int device) { error_flag(device).zero_(); }
 void bind_gemm(py::module_& m) {
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
-          py::arg("timeout_ms") = 2000.0);
+          py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none());
     m.def("build_plan", &build_plan);
     m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
     m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());

@@ -100,6 +100,9 @@ struct Fp8CastArgs {
     int32_t* scales_ue8m0;    // [M,hidden/512] packed exponents (when ue8m0 == 1)
     int num_rows, hidden;
     int round_scale, ue8m0;
+    // optional masking for grouped layouts: row r is cast only if (r % rows_per_group) < group_counts[r / rows_per_group]
+    const int* group_counts;
+    int rows_per_group;
 };
 cudaError_t launch_fp8_cast(const Fp8CastArgs& a, cudaStream_t stream);
 

@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(kCastThreads) fp8_cast_kernel(const Fp8CastArg
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (kCastThreads / 32) + (threadIdx.x >> 5);
     if (row >= a.num_rows) return;
+    if (a.group_counts != nullptr && (row % a.rows_per_group) >= a.group_counts[row / a.rows_per_group]) return;  // padding row
     const int H = a.hidden;
     const char* src = reinterpret_cast<const char*>(a.x) + (size_t)row * H * 2;
     uint8_t* dst = a.out + (size_t)row * H;

@@ -27,6 +27,8 @@ struct GroupedGemmArgs {
     const float* a_scales;    // fp8 only: [M_total, K/128]
     const float* b_scales;    // fp8 only: [G, N/128, K/128]
     const int* m_offsets;     // [G+1] device memory
+    const int* m_ends;        // optional [G]: group g covers rows [m_offsets[g], m_ends[g]) instead of up to m_offsets[g+1]
+                              // (mode 0 only; the low-latency layout has fixed group starts and a count per expert)
     int num_groups;
     int mode;                 // 0 = M-grouped, 1 = K-grouped
     int fp8;                  // 0 = bf16 operands, 1 = e4m3 operands (mode 0 only)

@@ -183,6 +183,7 @@ __device__ __forceinline__ void store_block_coalesced(int4* stage, const int4 (&
 
 struct TileInfo {
     int a_row, a_k0, b_row, b_row2, b_k0, num_kb, c_row, c_col, group, nblock, nblock2;
+    int c_row_end;  // first output row this tile must not write (end of its group; groups need no 128-row alignment)
 };
 
 template <int kBlockN, bool kFp8, bool kSwiGLU>
@@ -245,8 +246,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int g = 0; g < G; ++g) {
             tile_start[g] = run;
             if (p.mode == 0) {
-                const int rows = p.m_offsets[g + 1] - p.m_offsets[g];
-                run += ((rows + kBlockM - 1) / kBlockM) * tiles_n;
+                const int rows = (p.m_ends != nullptr ? p.m_ends[g] : p.m_offsets[g + 1]) - p.m_offsets[g];
+                run += ((max(rows, 0) + kBlockM - 1) / kBlockM) * tiles_n;
             } else {
                 run += tiles_fixed;
             }
@@ -266,7 +267,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     auto decode = [&](int tile, int& g, TileInfo& ti) {
         while (tile >= tile_start[g + 1]) ++g;
         const int local = tile - tile_start[g];
-        const int m0 = p.m_offsets[g], m1 = p.m_offsets[g + 1];
+        const int m0 = p.m_offsets[g], m1 = (p.mode == 0 && p.m_ends != nullptr) ? max(p.m_ends[g], m0) : p.m_offsets[g + 1];
         ti.group = g;
         if (p.mode == 0) {
             const int tiles_m = (m1 - m0 + kBlockM - 1) / kBlockM;
@@ -279,6 +280,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ti.b_k0 = 0;
             ti.num_kb = p.k / elem_per_kb;
             ti.c_row = ti.a_row;
+            ti.c_row_end = min(m1, p.m_total);
             if (kSwiGLU) {
                 const int half = kBlockN / 2, inter = p.n / 2;
                 ti.b_row = g * p.n + nt * half;            // gate rows
@@ -303,6 +305,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ti.b_k0 = m0;
             ti.num_kb = (m1 - m0) / elem_per_kb;
             ti.c_row = g * p.n + it * kBlockM;
+            ti.c_row_end = p.num_groups * p.n;
             ti.c_col = jt * kBlockN;
             ti.nblock = ti.nblock2 = 0;
         }
@@ -408,13 +411,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.c);
         const int ldc = p.mode == 0 ? (kSwiGLU ? p.n / 2 : p.n) : p.k;
-        const int c_rows = p.mode == 0 ? p.m_total : p.num_groups * p.n;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             decode(tile, g, ti);
             const int row = ti.c_row + row_in_tile;
             __nv_bfloat16* crow = cbase + (size_t)row * ldc + ti.c_col;
             if (ti.num_kb == 0) {
-                if (row < c_rows && half == 0)
+                if (row < ti.c_row_end && half == 0)
                     for (int c = 0; c < C::kOutCols; c += 8) *reinterpret_cast<int4*>(crow + c) = make_int4(0, 0, 0, 0);
                 continue;
             }
@@ -463,7 +465,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 {
                     // rows of this warp: ti.c_row + q*32 .. +32; the block base is row 0 of the warp
                     __nv_bfloat16* wbase = cbase + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
-                    const int rows_valid = min(32, c_rows - (ti.c_row + q * 32));
+                    const int rows_valid = min(32, ti.c_row_end - (ti.c_row + q * 32));
                     if constexpr (kSwiGLU) {
                         int4 regs[4];
 #pragma unroll
@@ -489,7 +491,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
                 __nv_bfloat16* wbase = cbase + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
-                const int rows_valid = min(32, c_rows - (ti.c_row + q * 32));
+                const int rows_valid = min(32, ti.c_row_end - (ti.c_row + q * 32));
                 if constexpr (kSwiGLU) {
 #pragma unroll 1
                     for (int c = 0; c < C::kOutCols; c += 32) {

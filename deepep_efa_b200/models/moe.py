@@ -197,6 +197,45 @@ class MoELayer(nn.Module):
         return out
 
 
+    # -- low-latency (decode) path ------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_low_latency(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
+                            num_max_tokens: Optional[int] = None) -> torch.Tensor:
+        """Decode-sized forward: low-latency dispatch (FP8 on the wire) -> masked grouped FP8 GEMMs over the
+        ``[L, N, hidden]`` landing zone (only the ``packed_recv_count[e]`` valid rows of every expert are computed) ->
+        the second GEMM writes straight into the zero-copy combine buffer -> low-latency combine. No host
+        synchronisation anywhere, so the whole layer can be captured in a CUDA graph."""
+        from .. import _ext
+        C = _ext.load()
+        if self._fp8 is None:
+            self.prepare_fp8()
+        (w13, s13), (w2, s2) = self._fp8
+        if topk_idx is None:
+            topk_idx, topk_weights = self.route(x)
+        buf, cfg = self.buffer, self.cfg
+        R, L = buf.group_size, self.num_local_experts
+        M = num_max_tokens or x.size(0)
+        N, H, I = R * M, cfg.hidden, cfg.intermediate
+        (px, ps), cnt, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, M, cfg.num_experts, use_fp8=True)
+        ws = self.__dict__.setdefault("_ll_ws", {})
+        key = (M, x.device)
+        if key not in ws:
+            dev = x.device
+            ws[key] = dict(starts=(torch.arange(L + 1, device=dev, dtype=torch.int32) * N).contiguous(),
+                           h=torch.empty(L * N, I, dtype=torch.bfloat16, device=dev),
+                           hq=torch.empty(L * N, I, dtype=torch.float8_e4m3fn, device=dev),
+                           hs=torch.empty(L * N, I // 128, dtype=torch.float32, device=dev))
+        w_ = ws[key]
+        ends = w_["starts"][:L] + cnt
+        a, a_s = px.view(L * N, H), ps.view(L * N, H // 128)
+        gg.grouped_gemm(a, w13, w_["starts"], swiglu=True, a_scales=a_s, b_scales=s13, out=w_["h"], m_ends=ends)
+        C.per_token_cast_to_fp8(w_["h"], False, False, cnt, N, w_["hq"], w_["hs"])
+        y = buf.get_next_low_latency_combine_buffer(handle)
+        gg.grouped_gemm(w_["hq"], w2, w_["starts"], a_scales=w_["hs"], b_scales=s2, out=y.view(L * N, H), m_ends=ends)
+        out, _, _ = buf.low_latency_combine(y, topk_idx, topk_weights, handle, zero_copy=True)
+        return out
+
+
 def dense_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w13_all: torch.Tensor, w2_all: torch.Tensor) -> torch.Tensor:
     """Single-process fp32 loop over all experts (w13_all [E, 2I, H], w2_all [E, H, I]); the oracle for the layer."""
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)

@@ -1,7 +1,10 @@
 """Grouped expert GEMM (tcgen05 / TMEM / TMA kernel in csrc/kernels/grouped_gemm.cu) and its autograd wrapper.
 
 ``grouped_gemm(a, b, m_offsets)`` computes ``c[m] = a[m] @ b[g].T`` for the rows m of expert g, where the rows of
-expert g are ``[m_offsets[g], m_offsets[g+1])`` and every boundary is a multiple of 128. Operands are bf16, or
+expert g are ``[m_offsets[g], m_offsets[g+1])`` (any boundaries: a tile never writes past its group's end; the
+K-grouped weight-gradient mode needs boundaries on multiples of 128). With ``m_ends`` only the rows
+``[m_offsets[g], m_ends[g])`` of every group are computed, which is how the low-latency ``[L, N, hidden]`` landing
+zone with its per-expert counts is consumed without compaction. Operands are bf16, or
 e4m3 with DeepSeek-style fp32 scales (1x128 on ``a``, 128x128 on ``b``). ``swiglu=True`` treats ``b`` as
 ``[G, 2*I, K]`` = [gate; up] and returns ``silu(a @ gate.T) * (a @ up.T)``.
 
@@ -19,9 +22,13 @@ from .. import _ext
 
 def grouped_gemm(a: torch.Tensor, b: torch.Tensor, m_offsets: torch.Tensor, *, swiglu: bool = False,
                  a_scales: Optional[torch.Tensor] = None, b_scales: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
-    """M-grouped GEMM; see the module docstring. Returns bf16 ``[M, N]`` (``[M, N/2]`` with ``swiglu``)."""
-    return _ext.load().grouped_gemm(a, b, m_offsets, 0, swiglu, a_scales, b_scales, out, num_sms)
+                 out: Optional[torch.Tensor] = None, num_sms: int = 0, m_ends: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """M-grouped GEMM; see the module docstring. Returns bf16 ``[M, N]`` (``[M, N/2]`` with ``swiglu``).
+
+    ``m_ends`` (int32 ``[G]``, optional) makes group g cover rows ``[m_offsets[g], m_ends[g])``: the "masked" form for the
+    low-latency layout ``[L, N, hidden]``, where every expert starts at ``g * N`` and only ``packed_recv_count[g]`` rows
+    are valid. Rows of a partly filled last tile are computed and written too (they are padding by contract)."""
+    return _ext.load().grouped_gemm(a, b, m_offsets, 0, swiglu, a_scales, b_scales, out, num_sms, 2000.0, m_ends)
 
 
 def grouped_gemm_wgrad(a_t: torch.Tensor, b_t: torch.Tensor, m_offsets: torch.Tensor, *, out: Optional[torch.Tensor] = None,

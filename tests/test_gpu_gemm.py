@@ -37,6 +37,46 @@ def test_bf16_mgrouped(rows, K, N):
     assert torch.equal(c, c2)
 
 
+def test_unaligned_and_masked_groups():
+    """Group boundaries anywhere, and m_ends: only the first rows of every group are computed, the rest stay untouched."""
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm, reference_grouped_gemm
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(5)
+    rows, K, N = [40, 200, 0, 77, 3], 256, 256
+    G, M = len(rows), sum(rows)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(G, N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    offs = _offsets(rows)
+    c = grouped_gemm(a, b, offs)
+    ref = reference_grouped_gemm(a, b, offs)
+    assert _rel_err(c, ref) < 1e-2, _rel_err(c, ref)
+    # masked: fixed stride 64 per group (tiles of 128 rows overlap the next group), counts 0..64
+    stride, counts = 64, [64, 0, 17, 33, 1]
+    starts = torch.arange(G + 1, device="cuda", dtype=torch.int32) * stride
+    ends = starts[:G] + torch.tensor(counts, device="cuda", dtype=torch.int32)
+    a = torch.randn(G * stride, K, device="cuda").to(torch.bfloat16)
+    out = torch.full((G * stride, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    grouped_gemm(a, b, starts, out=out, m_ends=ends)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    full = reference_grouped_gemm(a, b, starts)
+    for g, n in enumerate(counts):
+        lo = g * stride
+        if n:
+            assert _rel_err(out[lo:lo + n], full[lo:lo + n]) < 1e-2
+        assert (out[lo + n:lo + stride] == 7.0).all()
+    sw = torch.full((G * stride, N // 2), 7.0, device="cuda", dtype=torch.bfloat16)
+    grouped_gemm(a, b, starts, swiglu=True, out=sw, m_ends=ends)
+    fsw = reference_grouped_gemm(a, b, starts, swiglu=True)
+    for g, n in enumerate(counts):
+        lo = g * stride
+        if n:
+            assert _rel_err(sw[lo:lo + n], fsw[lo:lo + n]) < 1.5e-2
+        assert (sw[lo + n:lo + stride] == 7.0).all()
+
+
 @pytest.mark.parametrize("rows,K,I", [([128, 256], 256, 128), ([128, 128, 384], 512, 192)])
 def test_bf16_swiglu(rows, K, I):
     from deepep_efa_b200.ops.grouped_gemm import grouped_gemm, reference_grouped_gemm

@@ -78,3 +78,25 @@ def test_moe_layer_forward_backward_gpu():
         assert _rel(y8, ref.detach()) < 8e-2, _rel(y8, ref.detach())
     finally:
         vc.destroy()
+
+
+def test_moe_low_latency_decode_path():
+    import deepep_efa_b200 as ep
+    from deepep_efa_b200.models.moe import MoEConfig, MoELayer, dense_reference
+    from deepep_efa_b200.parallel.virtual import VirtualCluster
+    T, H, I, E, K = 48, 512, 256, 8, 2
+    vc = VirtualCluster(1, num_nvl_bytes=8 << 20, num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(64, H, 1, E))
+    try:
+        buf = vc.buffers[0]
+        layer = MoELayer(MoEConfig(hidden=H, intermediate=I, num_experts=E, num_topk=K, init_std=0.05), buf)
+        x = make_tokens(T, H, "cuda", seed=5)
+        idx, w = make_routing(T, E, K, "cuda", seed=5, masked_fraction=0.1)
+        ref = dense_reference(x, idx, w.masked_fill(idx == -1, 0), layer.w13.detach().float(), layer.w2.detach().float())
+        for _ in range(3):  # both parities, workspace reuse
+            y = layer.forward_low_latency(x, idx, w, num_max_tokens=64)
+            torch.cuda.synchronize()
+            buf.check_status()
+            assert ep._ext.load().gemm_error(0) == 0
+            assert _rel(y, ref) < 8e-2, _rel(y, ref)
+    finally:
+        vc.destroy()

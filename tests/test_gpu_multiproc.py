@@ -151,6 +151,11 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         buf.check_status()
         assert rel(y8, ref.detach()) < 8e-2, rel(y8, ref.detach())
+        align()
+        yl = layer.forward_low_latency(xm.detach(), mi, mw, num_max_tokens=T)
+        torch.cuda.synchronize()
+        buf.check_status()
+        assert rel(yl, ref.detach()) < 8e-2, rel(yl, ref.detach())
         buf.destroy()
         dist.destroy_process_group()
         q.put((rank, "ok"))

@@ -33,10 +33,12 @@ CUDA_SOURCES = [
     "kernels/grouped_gemm.cu",
     "kernels/permute.cu",
     "kernels/noalloc.cu",
+    "kernels/hier.cu",
 ]
 CPP_SOURCES = [
     "host/bindings.cpp",
     "host/gemm_bindings.cpp",
+    "host/hier_bindings.cpp",
 ]
 
 CUDA_FLAGS = [

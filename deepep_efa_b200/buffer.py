@@ -67,7 +67,8 @@ class Buffer:
                  low_latency_mode: bool = False, num_qps_per_rank: int = 24,
                  allow_nvlink_for_low_latency_mode: bool = True, allow_mnnvl: bool = False, use_fabric: bool = False,
                  explicitly_destroy: bool = False, enable_shrink: bool = False, comm=None, *,
-                 timeout_ms: Optional[float] = None, _virtual: Optional[Tuple[int, int]] = None) -> None:
+                 timeout_ms: Optional[float] = None, num_nvl_ranks: Optional[int] = None,
+                 _virtual: Optional[Tuple[int, int]] = None) -> None:
         """Create the buffer and exchange peer mappings (collective over ``group``).
 
         Arguments follow the reference (deep_ep/buffer.py:99-131). ``num_qps_per_rank``,
@@ -75,6 +76,10 @@ class Buffer:
         fabric transports of the reference and are accepted and ignored on a single NVSwitch box.
         ``timeout_ms`` bounds every device-side wait (default: env ``DEEPEP_TIMEOUT_MS`` or 10 s).
         ``enable_shrink`` makes low-latency waits mask a silent rank instead of failing the call.
+        ``num_nvl_ranks`` (default: env ``DEEPEP_NVL_DOMAIN_SIZE`` or 8) is the size of one NVLink domain; a larger
+        group runs the two-level path of :mod:`deepep_efa_b200.parallel.internode` (NVLink kernels inside every
+        domain, collectives between them), where the reference uses NCCL + libfabric/EFA
+        (deep_ep/buffer.py:193-226, 582-1560).
         """
         self.num_nvl_bytes = int(num_nvl_bytes)
         self.num_rdma_bytes = int(num_rdma_bytes)
@@ -86,6 +91,8 @@ class Buffer:
         self._ll_cache = {}
         self._ll_parity = 0
         self._virtual_peers: Optional[List["Buffer"]] = None
+        self._hier = None
+        self._ll_mask_local = None
 
         if _virtual is not None:
             self.rank, self.group_size = _virtual
@@ -106,10 +113,20 @@ class Buffer:
         else:
             raise ValueError("Either 'group' or 'comm' must be provided.")
 
-        if self.group_size > 8:
-            raise NotImplementedError(
-                "more than 8 ranks means more than one NVSwitch domain: the multi-node (EFA/RDMA) transport of the "
-                "reference is a documented stub in this library (see internode_dispatch)")
+        nvl = int(num_nvl_ranks if num_nvl_ranks is not None else os.environ.get("DEEPEP_NVL_DOMAIN_SIZE", "8"))
+        assert 1 <= nvl <= 8, "an NVLink domain of this library has at most 8 ranks"
+        if _virtual is None and self.group_size > nvl:
+            if group is None:
+                raise NotImplementedError("groups larger than one NVLink domain need a torch.distributed process group")
+            from .parallel.internode import HierarchicalEP
+            self.runtime = None
+            self._hier = HierarchicalEP(group, nvl, lambda g: Buffer(
+                g, num_nvl_bytes, num_rdma_bytes, low_latency_mode, num_qps_per_rank, allow_nvlink_for_low_latency_mode, allow_mnnvl,
+                use_fabric, True, enable_shrink, timeout_ms=timeout_ms, num_nvl_ranks=nvl))
+            nb = self._hier.node_buf
+            if nb._cpu is None:
+                self._C, self.device, self.comm_stream = nb._C, nb.device, nb.comm_stream
+            return
 
         if not torch.cuda.is_available():
             # CPU ranks (gloo): pure-PyTorch backend with the same semantics.
@@ -143,6 +160,9 @@ class Buffer:
         if self._destroyed:
             return
         self._destroyed = True
+        if self._hier is not None:
+            self._hier.destroy()
+            return
         if self._cpu is not None or self.runtime is None:
             return
         torch.cuda.synchronize()
@@ -190,21 +210,30 @@ class Buffer:
 
     # Accessors of the reference's runtime object (csrc/deep_ep.cpp:308-358), answered for one NVSwitch domain.
     def is_available(self) -> bool:
+        if self._hier is not None:
+            return self._hier.node_buf.is_available()
         return self._cpu is not None or (self.runtime is not None and self.runtime.is_available())
 
     def get_num_rdma_ranks(self) -> int:
-        return 1
+        """Number of NVLink domains of the group (the reference's ``num_rdma_ranks``, csrc/deep_ep.cpp:243-244)."""
+        return self._hier.num_nodes if self._hier is not None else 1
 
     def get_rdma_rank(self) -> int:
-        return 0
+        return self._hier.node if self._hier is not None else 0
 
     def get_root_rdma_rank(self, global_: bool = True) -> int:
-        return 0
+        if self._hier is None:
+            return 0
+        return self._hier.node * self._hier.P if global_ else 0
 
     def get_local_device_id(self) -> int:
+        if self._hier is not None:
+            return self._hier.node_buf.get_local_device_id()
         return self.device.index if self._cpu is None else -1
 
     def get_local_ipc_handle(self) -> bytes:
+        if self._hier is not None:
+            return self._hier.node_buf.get_local_ipc_handle()
         return bytes(self.runtime.ipc_handle())
 
     def get_comm_stream(self) -> "torch.cuda.Stream":
@@ -213,6 +242,8 @@ class Buffer:
     def get_local_buffer_tensor(self, dtype: torch.dtype, size: Optional[torch.Size] = None, offset: int = 0,
                                 use_rdma_buffer: bool = False) -> torch.Tensor:
         """A view of this rank's symmetric memory: the arena part (default) or the low-latency region."""
+        if self._hier is not None:
+            return self._hier.node_buf.get_local_buffer_tensor(dtype, size, offset, use_rdma_buffer)
         ctrl = self._C.CONTROL_BYTES
         base = ctrl if use_rdma_buffer else ctrl + self.runtime.ll_bytes()
         total = self.runtime.ll_bytes() if use_rdma_buffer else self.runtime.total_bytes() - base
@@ -224,6 +255,8 @@ class Buffer:
     def empty_symmetric(self, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         """Allocate a tensor inside this rank's peer-mapped arena. A combine whose input lives there is
         zero-copy; anything else is staged through one local copy first."""
+        if self._hier is not None:
+            return self._hier.node_buf.empty_symmetric(shape, dtype)
         return self.runtime.alloc_symmetric(list(shape), dtype)
 
     @staticmethod
@@ -255,6 +288,8 @@ class Buffer:
     # ------------------------------------------------------------------------------------------
     def check_status(self, sync: bool = False) -> None:
         """Raise :class:`EPTimeoutError` if a kernel of this buffer reported a timed-out wait."""
+        if self._hier is not None:
+            return self._hier.node_buf.check_status(sync)
         if self.runtime is None:
             return
         if sync:
@@ -264,6 +299,8 @@ class Buffer:
 
     def recover(self) -> None:
         """Collective reset after an error: zero the control block and all sequence state."""
+        if self._hier is not None:
+            return self._hier.node_buf.recover()
         if self.runtime is None:
             return
         _log(_logging.WARNING, self.rank, f"recovering buffer after: {self.runtime.status_string()}")
@@ -283,10 +320,13 @@ class Buffer:
         """Count tokens per rank / expert and build the membership matrix.
 
         Returns ``(num_tokens_per_rank[R] i32, None, num_tokens_per_expert[E] i32, is_token_in_rank[T,R] bool,
-        event)``; the second entry (tokens per RDMA rank) is always ``None`` inside one NVSwitch domain
-        (deep_ep/buffer.py:422-448).
+        event)``; the second entry (tokens per RDMA rank = per NVLink domain, i32 ``[domains]``) is ``None`` when the
+        group is a single NVLink domain (deep_ep/buffer.py:422-448).
         """
         topk_idx = _as_topk_idx(topk_idx)
+        if self._hier is not None:
+            _wait_previous(previous_event)
+            return self._hier.get_dispatch_layout(topk_idx, num_experts)
         if self._cpu is not None:
             a, b, c = self._cpu.get_dispatch_layout(topk_idx, num_experts)
             return a, None, b, c, EventOverlap()
@@ -318,6 +358,11 @@ class Buffer:
         tensors live in this rank's symmetric arena; their memory returns to the arena when they die.
         """
         topk_idx = _as_topk_idx(topk_idx)
+        if self._hier is not None:
+            return self.internode_dispatch(x, handle, num_tokens_per_rank, num_tokens_per_rdma_rank, is_token_in_rank,
+                                           num_tokens_per_expert, topk_idx, topk_weights, expert_alignment, num_worst_tokens, config,
+                                           previous_event, async_finish, allocate_on_comm_stream, quantize_fp8=quantize_fp8,
+                                           round_scale=round_scale)
         if self._cpu is not None:
             return self._cpu.dispatch(x, handle, num_tokens_per_rank, is_token_in_rank, num_tokens_per_expert, topk_idx,
                                       topk_weights, expert_alignment, num_worst_tokens)
@@ -336,23 +381,45 @@ class Buffer:
         If ``x`` already lives in the symmetric arena (a dispatch result, or a tensor from
         :meth:`empty_symmetric`) it is read in place by the peers; otherwise it is staged with one local copy.
         """
+        if self._hier is not None:
+            return self.internode_combine(x, handle, topk_weights, bias, config, previous_event, async_finish, allocate_on_comm_stream)
         if self._cpu is not None:
             return self._cpu.combine(x, handle, topk_weights, bias)
         config = self.get_combine_config(self.group_size) if config is None else config
         return _combine_many([self], [(x, handle, topk_weights, bias)], config, previous_event, async_finish,
                              allocate_on_comm_stream)[0]
 
-    # Multi-node paths: a documented stub on one NVSwitch box.
-    def internode_dispatch(self, *args, **kwargs):
-        """The reference implements multi-node dispatch in Python over NCCL + libfabric/EFA
-        (deep_ep/buffer.py:582-861). One NVSwitch domain has no second node, so this raises."""
-        raise NotImplementedError("multi-node (EFA/RDMA) dispatch is out of scope on a single NVSwitch box; "
-                                  "use dispatch() with up to 8 ranks")
+    # Groups that span several NVLink domains (the reference's "internode" paths).
+    def internode_dispatch(self, x, handle: Optional[Tuple] = None, num_tokens_per_rank: Optional[torch.Tensor] = None,
+                           num_tokens_per_rdma_rank: Optional[torch.Tensor] = None, is_token_in_rank: Optional[torch.Tensor] = None,
+                           num_tokens_per_expert: Optional[torch.Tensor] = None, topk_idx: Optional[torch.Tensor] = None,
+                           topk_weights: Optional[torch.Tensor] = None, expert_alignment: int = 1, num_worst_tokens: int = 0,
+                           config: Optional[Config] = None, previous_event: Optional[EventOverlap] = None, async_finish: bool = False,
+                           allocate_on_comm_stream: bool = False, *, quantize_fp8: bool = False, round_scale: bool = False):
+        """Dispatch across NVLink domains: one rail hop per destination domain, then the NVLink dispatch kernel inside the
+        domain (see :mod:`deepep_efa_b200.parallel.internode`). Same arguments and return tuple as the reference
+        (deep_ep/buffer.py:582-861); the handle is a self-contained 10-tuple. ``dispatch`` routes here automatically when
+        the group is larger than one NVLink domain. Work is issued on the current stream; ``event`` marks its end."""
+        if self._hier is None:
+            raise NotImplementedError("this group is a single NVLink domain: use dispatch()")
+        _wait_previous(previous_event)
+        config = self.get_dispatch_config(self._hier.P) if config is None else config
+        out = self._hier.dispatch(x, handle, num_tokens_per_rank, num_tokens_per_rdma_rank, is_token_in_rank, num_tokens_per_expert,
+                                  _as_topk_idx(topk_idx), topk_weights, expert_alignment, num_worst_tokens, config, quantize_fp8, round_scale)
+        return out[:5] + (_end_event(self),)
 
-    def internode_combine(self, *args, **kwargs):
-        """See :meth:`internode_dispatch` (reference: deep_ep/buffer.py:1437-1560)."""
-        raise NotImplementedError("multi-node (EFA/RDMA) combine is out of scope on a single NVSwitch box; "
-                                  "use combine() with up to 8 ranks")
+    def internode_combine(self, x: torch.Tensor, handle: Tuple, topk_weights: Optional[torch.Tensor] = None,
+                          bias: Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor], None] = None, config: Optional[Config] = None,
+                          previous_event: Optional[EventOverlap] = None, async_finish: bool = False,
+                          allocate_on_comm_stream: bool = False):
+        """Combine across NVLink domains: NVLink reduction per domain, one partial per domain back over the rail, fp32 sum
+        at the home rank (reference: deep_ep/buffer.py:1437-1560)."""
+        if self._hier is None:
+            raise NotImplementedError("this group is a single NVLink domain: use combine()")
+        _wait_previous(previous_event)
+        config = self.get_combine_config(self._hier.P) if config is None else config
+        out, out_w, _ = self._hier.combine(x, handle, topk_weights, bias, config)
+        return out, out_w, _end_event(self)
 
     # ------------------------------------------------------------------------------------------
     # low-latency mode
@@ -360,7 +427,7 @@ class Buffer:
     def clean_low_latency_buffer(self, num_max_dispatch_tokens_per_rank: int = 0, hidden: int = 0, num_experts: int = 0) -> None:
         """Collective reset of all signalling state. Sequence numbers are monotonic, so this is only
         needed after an error or a shrink event (reference: deep_ep/buffer.py:1562-1584)."""
-        if self._cpu is not None:
+        if self._cpu is not None or self._hier is not None:
             return
         self.recover()
 
@@ -410,6 +477,11 @@ class Buffer:
         With ``return_recv_hook`` only the send half runs now and ``hook()`` launches the receive half.
         """
         topk_idx = _as_topk_idx(topk_idx)
+        if self._hier is not None:
+            # across NVLink domains: the collective fallback (count exchange, packed rows, one all-to-all, scatter)
+            rx, cnt, h, _, _ = self._hier.low_latency_dispatch(x, topk_idx, num_max_dispatch_tokens_per_rank, num_experts, use_fp8,
+                                                               round_scale, use_ue8m0, cumulative_local_expert_recv_stats)
+            return rx, cnt, h, _end_event(self), ((lambda: None) if return_recv_hook else None)
         if self._cpu is not None:
             return self._cpu.low_latency_dispatch(x, topk_idx, num_max_dispatch_tokens_per_rank, num_experts, use_fp8,
                                                   round_scale, use_ue8m0, cumulative_local_expert_recv_stats, return_recv_hook)
@@ -438,6 +510,11 @@ class Buffer:
         ``use_logfmt`` (a 10-bit wire format of upstream DeepEP) is accepted and ignored: rows travel as bf16.
         """
         topk_idx = _as_topk_idx(topk_idx)
+        if self._hier is not None:
+            if zero_copy:
+                x = self.get_next_low_latency_combine_buffer(handle)
+            res, _, _ = self._hier.low_latency_combine(x, topk_idx, topk_weights, handle, out)
+            return res, _end_event(self), ((lambda: None) if return_recv_hook else None)
         if self._cpu is not None:
             return self._cpu.low_latency_combine(x, topk_idx, topk_weights, handle, out, return_recv_hook)
         assert not (async_finish and return_recv_hook)
@@ -455,7 +532,13 @@ class Buffer:
     def get_next_low_latency_combine_buffer(self, handle: tuple) -> torch.Tensor:
         """The symmetric ``[L, N, hidden]`` bf16 buffer the next ``low_latency_combine(..., zero_copy=True)`` with
         this handle reads; let the expert GEMM write its output here (deep_ep/buffer.py:2831-2852)."""
-        src_info, _, num_max_tokens, hidden, num_experts = handle
+        src_info, _, num_max_tokens, hidden, num_experts = handle[:5]
+        if self._hier is not None:
+            key = ("hier_combine_src", num_max_tokens, hidden, num_experts)
+            if key not in self._ll_cache:
+                self._ll_cache[key] = torch.empty(num_experts // self.group_size, self.group_size * num_max_tokens, hidden,
+                                                  dtype=torch.bfloat16, device=src_info.device)
+            return self._ll_cache[key]
         if self._cpu is not None:
             return self._cpu.get_next_low_latency_combine_buffer(handle)
         views = self._ll_views(num_max_tokens, hidden, num_experts)
@@ -465,16 +548,31 @@ class Buffer:
         """Mask (or unmask) a rank: low-latency kernels stop sending to it and stop waiting for it. The mask is
         device memory the kernels read (the reference keeps a Python-side tensor no kernel consults,
         deep_ep/buffer.py:2805-2829)."""
+        if self._hier is not None:
+            # across NVLink domains the collective fallback has no waits to shorten: the mask is recorded and reported only
+            self._hier_mask()[rank_to_mask] = 1 if mask else 0
+            return
         if self._cpu is not None:
             return self._cpu.update_mask(rank_to_mask, mask)
         self.runtime.set_mask(rank_to_mask, mask)
 
+    def _hier_mask(self) -> torch.Tensor:
+        if self._ll_mask_local is None:
+            self._ll_mask_local = torch.zeros(self.group_size, dtype=torch.int32)
+        return self._ll_mask_local
+
     def low_latency_query_mask_buffer(self, mask_status: torch.Tensor) -> None:
+        if self._hier is not None:
+            mask_status.copy_(self._hier_mask())
+            return
         if self._cpu is not None:
             return self._cpu.query_mask(mask_status)
         self.runtime.query_mask(mask_status)
 
     def low_latency_clean_mask_buffer(self) -> None:
+        if self._hier is not None:
+            self._hier_mask().zero_()
+            return
         if self._cpu is not None:
             return self._cpu.clean_mask()
         self.runtime.clean_mask()
@@ -487,6 +585,15 @@ class Buffer:
 # ================================================================================================
 # helpers shared by the single-rank API above and the single-GPU multi-rank emulation
 # ================================================================================================
+def _wait_previous(previous_event) -> None:
+    if previous_event is not None:
+        previous_event.current_stream_wait()
+
+
+def _end_event(buf) -> EventOverlap:
+    return EventOverlap(EventHandle()) if torch.cuda.is_available() else EventOverlap()
+
+
 def _as_topk_idx(topk_idx):
     """The kernels take int64 expert ids (``topk_idx_t``); int32 ids (the reference's TOPK_IDX_BITS=32 build,
     csrc/kernels/configs.cuh:66-72) are widened."""

@@ -19,12 +19,15 @@ DISPATCH_CONFIGS = {
     2: (32, 6, 256, 6, 128),
     4: (32, 6, 256, 6, 128),
     8: (32, 6, 256, 6, 128),
+    # several NVLink domains: the config drives the node-level NVLink kernels of the two-level path
+    16: (32, 6, 256, 6, 128), 24: (32, 6, 256, 6, 128), 32: (32, 6, 256, 6, 128), 48: (32, 6, 256, 6, 128), 64: (32, 6, 256, 6, 128),
 }
 COMBINE_CONFIGS = {
     1: (32, 4, 256, 6, 128),
     2: (32, 4, 256, 6, 128),
     4: (32, 4, 256, 6, 128),
     8: (32, 4, 256, 6, 128),
+    16: (32, 4, 256, 6, 128), 24: (32, 4, 256, 6, 128), 32: (32, 4, 256, 6, 128), 48: (32, 4, 256, 6, 128), 64: (32, 4, 256, 6, 128),
 }
 
 

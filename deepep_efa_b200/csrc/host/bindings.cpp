@@ -156,7 +156,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> get_dispatch_layout(Runt
     auto in_rank = torch::empty({T, R}, i32.dtype(torch::kBool));
     const int64_t need = (int64_t)dx::layout_scratch_ints(num_experts, R, T);
     if (!rt->layout_scratch.defined() || rt->layout_scratch.numel() < need) rt->layout_scratch = torch::zeros({need}, i32);
-    dx::LayoutArgs a;
+    dx::LayoutArgs a{};
     a.topk_idx = topk_idx.data_ptr<int64_t>();
     a.num_tokens = T;
     a.num_topk = K;
@@ -561,6 +561,7 @@ py::dict ll_layout(Runtime* rt, int num_max_tokens, int hidden, int num_experts)
 }  // namespace
 
 void bind_gemm(py::module_& m);  // gemm_bindings.cpp
+void bind_hier(py::module_& m);  // hier_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "deepep_efa_b200 native runtime (sm_100a)";
@@ -653,4 +654,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ll_combine", &ll_combine);
     m.def("ll_layout", &ll_layout);
     bind_gemm(m);
+    bind_hier(m);
 }

@@ -28,8 +28,11 @@ struct LayoutArgs {
     int* num_tokens_per_expert;   // [E]
     bool* is_token_in_rank;       // [T,R]
     int* scratch;                 // >= layout_scratch_ints(E,R,T) ints, first int must be 0 between calls
+    // groups that span several NVLink domains: R <= 64 ranks in domains of ranks_per_node; 0 = single domain
+    int ranks_per_node;
+    int* num_tokens_per_node;     // [R / ranks_per_node] or nullptr
 };
-size_t layout_scratch_ints(int num_experts, int num_ranks, int num_tokens);
+size_t layout_scratch_ints(int num_experts, int num_ranks, int num_tokens, int num_nodes = 0);
 cudaError_t launch_layout(const LayoutArgs& a, cudaStream_t stream);
 
 // ---- normal mode --------------------------------------------------------------------------
@@ -91,6 +94,43 @@ cudaError_t launch_barrier(const BarrierArgs* a, int num_virtual, cudaStream_t s
 // A wait that nothing satisfies, with the caller's (short) limit: proves that a timed-out wait sets
 // the status word and returns instead of hanging.
 cudaError_t launch_timeout_probe(const RankCtx& ctx, uint64_t* never_set_flag, cudaStream_t stream);
+
+// ---- two-level (NVLink domain x rail) bookkeeping, hier.cu ----------------------------------
+struct RoutingSortArgs {
+    const bool* member;   // [T, G * ranks_per_group]: token t goes to group g if any of the group's ranks is set
+    int num_tokens, num_groups, ranks_per_group;
+    int* sorted_ids;      // [sum counts] token ids ordered by (group, token)
+    int* counts;          // [G]
+    int* prefix;          // [G+1] exclusive prefix of counts
+    int* pos;             // [T, G] slot of (t, g) in sorted_ids or -1; may be nullptr
+};
+cudaError_t launch_routing_sort(const RoutingSortArgs& a, cudaStream_t stream);
+
+struct TopkRemapArgs {
+    const int64_t* topk_idx;     // [T, K] global expert ids, -1 = unselected
+    const float* topk_weights;   // [T, K] or nullptr
+    const int* sorted_ids;       // [S]
+    const int* prefix;           // [G+1]
+    int num_entries, num_topk, num_groups, experts_per_group;
+    uint8_t* packed;             // [S, K*12]: K int64 group-relative ids (or -1), then K f32 weights (or 0)
+};
+cudaError_t launch_topk_remap_pack(const TopkRemapArgs& a, cudaStream_t stream);
+
+struct RecvSrcMetaArgs {
+    const int* recv_prefix;            // [G+1] exclusive prefix of rows received per source group
+    const bool* is_row_in_local_rank;  // [n, P] or nullptr
+    int num_rows, num_groups, num_local_ranks;
+    int* meta;                         // [n, 2] = (source group, bitmask of local ranks)
+};
+cudaError_t launch_recv_src_meta(const RecvSrcMetaArgs& a, cudaStream_t stream);
+
+struct SegmentedCopyArgs {
+    const uint8_t* src;
+    uint8_t* dst;
+    const int64_t* segments;  // [n, 3] = (src byte offset, dst byte offset, bytes)
+    int num_segments;
+};
+cudaError_t launch_segmented_copy(const SegmentedCopyArgs& a, cudaStream_t stream);
 
 // ---- standalone FP8 cast ------------------------------------------------------------------
 struct Fp8CastArgs {

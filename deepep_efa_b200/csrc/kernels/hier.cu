@@ -1,0 +1,164 @@
+// Bookkeeping kernels of the two-level (NVLink domain x rail) expert-parallel path.
+//
+// When a group spans several NVLink domains, a token crosses the inter-domain network once per destination
+// DOMAIN (to the rank with the sender's local index there) and is fanned out inside that domain by the NVLink
+// dispatch kernel. These kernels build the send plan of the first hop and the metadata of the second one:
+//
+//   routing_sort      stable counting sort of (token, destination group) pairs by group      -> sorted ids, counts,
+//                     exclusive prefix, and the inverse map pos[t, g]
+//   topk_remap_pack   per send entry: expert ids relative to the destination group (or -1) and weights (or 0),
+//                     packed as one row [K x int64 | K x f32] so that one collective carries both
+//   recv_src_meta     per received row: (source group, bitmask of the local ranks it is forwarded to)
+//   segmented_copy    byte-granular copy of a list of (src offset, dst offset, bytes) segments
+//
+// Reference counterparts (csrc/kernels/efa_kernels.cu): moe_routing_sort_kernel + prefix_sum_kernel +
+// scatter_token_ids_kernel (:220-318, three launches, the last one single-threaded per rank, ending in a host
+// sync), topk_remap_kernel (:339-387), build_recv_src_meta_kernel (:448-482), efa_permute_kernel (:405-435).
+// Here the sort is one launch without atomics or host round trip, and every CTA derives its own base offset.
+#include "api.h"
+#include "prims.cuh"
+
+namespace dx {
+
+constexpr int kSortThreads = 1024;
+
+__device__ __forceinline__ bool in_group(const bool* member, int t, int g, int ranks_total, int ranks_per_group) {
+    const bool* row = member + (size_t)t * ranks_total + (size_t)g * ranks_per_group;
+    bool any = false;
+    for (int j = 0; j < ranks_per_group; ++j) any |= row[j];
+    return any;
+}
+
+__global__ void __launch_bounds__(kSortThreads) routing_sort_kernel(const RoutingSortArgs a) {
+    __shared__ int s_warp[32];
+    __shared__ int s_base, s_own;
+    const int g = blockIdx.x, G = a.num_groups, T = a.num_tokens;
+    const int ranks_total = G * a.ranks_per_group;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // pass 1: how many pairs sort before this group's first entry, and how many entries the group has
+    int before = 0, own = 0;
+    for (int t = threadIdx.x; t < T; t += kSortThreads) {
+        for (int c = 0; c < g; ++c) before += in_group(a.member, t, c, ranks_total, a.ranks_per_group) ? 1 : 0;
+        own += in_group(a.member, t, g, ranks_total, a.ranks_per_group) ? 1 : 0;
+    }
+    before = warp_sum(before);
+    own = warp_sum(own);
+    if (threadIdx.x == 0) {
+        s_base = 0;
+        s_own = 0;
+    }
+    __syncthreads();
+    if (lane == 0) {
+        atomicAdd(&s_base, before);
+        atomicAdd(&s_own, own);
+    }
+    __syncthreads();
+    const int base = s_base;
+    if (threadIdx.x == 0) {
+        a.counts[g] = s_own;
+        a.prefix[g] = base;
+        if (g == G - 1) a.prefix[G] = base + s_own;
+    }
+
+    // pass 2: ordered scatter of this group's tokens
+    int running = base;
+    for (int t0 = 0; t0 < T; t0 += kSortThreads) {
+        const int t = t0 + threadIdx.x;
+        const bool flag = t < T && in_group(a.member, t, g, ranks_total, a.ranks_per_group);
+        const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+        __syncthreads();  // s_warp of the previous chunk has been read
+        if (lane == 0) s_warp[warp] = __popc(ballot);
+        __syncthreads();
+        int warp_off = 0, chunk_total = 0;
+        for (int w = 0; w < kSortThreads / 32; ++w) {
+            const int c = s_warp[w];
+            if (w < warp) warp_off += c;
+            chunk_total += c;
+        }
+        if (t < T) {
+            const int slot = running + warp_off + __popc(ballot & ((1u << lane) - 1u));
+            if (flag) a.sorted_ids[slot] = t;
+            if (a.pos != nullptr) a.pos[(size_t)t * G + g] = flag ? slot : -1;
+        }
+        running += chunk_total;
+    }
+}
+
+cudaError_t launch_routing_sort(const RoutingSortArgs& a, cudaStream_t stream) {
+    if (a.num_groups < 1 || a.ranks_per_group < 1) return cudaErrorInvalidValue;
+    routing_sort_kernel<<<a.num_groups, kSortThreads, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+// group of send entry s: the last g with prefix[g] <= s (prefix has G+1 entries, G <= 64: a linear scan)
+__device__ __forceinline__ int group_of_entry(const int* prefix, int G, int s) {
+    int g = 0;
+    while (g + 1 < G && __ldg(prefix + g + 1) <= s) ++g;
+    return g;
+}
+
+__global__ void topk_remap_pack_kernel(const TopkRemapArgs a) {
+    const int K = a.num_topk;
+    const size_t row_bytes = (size_t)K * 12;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)a.num_entries * K; i += (long long)gridDim.x * blockDim.x) {
+        const int s = (int)(i / K), k = (int)(i % K);
+        const int t = a.sorted_ids[s];
+        const int g = group_of_entry(a.prefix, a.num_groups, s);
+        const int64_t lo = (int64_t)g * a.experts_per_group;
+        const int64_t e = a.topk_idx[(size_t)t * K + k];
+        const bool mine = e >= lo && e < lo + a.experts_per_group;
+        uint8_t* row = a.packed + (size_t)s * row_bytes;
+        reinterpret_cast<int64_t*>(row)[k] = mine ? e - lo : -1;
+        reinterpret_cast<float*>(row + (size_t)K * 8)[k] = (mine && a.topk_weights != nullptr) ? a.topk_weights[(size_t)t * K + k] : 0.f;
+    }
+}
+
+cudaError_t launch_topk_remap_pack(const TopkRemapArgs& a, cudaStream_t stream) {
+    const long long n = (long long)a.num_entries * a.num_topk;
+    if (n == 0) return cudaSuccess;
+    const int blocks = (int)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048);
+    topk_remap_pack_kernel<<<blocks, 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+__global__ void recv_src_meta_kernel(const RecvSrcMetaArgs a) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.num_rows; i += gridDim.x * blockDim.x) {
+        const int g = group_of_entry(a.recv_prefix, a.num_groups, i);
+        int bits = 0;
+        if (a.is_row_in_local_rank != nullptr)
+            for (int j = 0; j < a.num_local_ranks; ++j) bits |= (a.is_row_in_local_rank[(size_t)i * a.num_local_ranks + j] ? 1 : 0) << j;
+        a.meta[2 * (size_t)i] = g;
+        a.meta[2 * (size_t)i + 1] = bits;
+    }
+}
+
+cudaError_t launch_recv_src_meta(const RecvSrcMetaArgs& a, cudaStream_t stream) {
+    if (a.num_rows == 0) return cudaSuccess;
+    const int blocks = (a.num_rows + 255) / 256 < 1024 ? (a.num_rows + 255) / 256 : 1024;
+    recv_src_meta_kernel<<<blocks, 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+__global__ void segmented_copy_kernel(const SegmentedCopyArgs a) {
+    for (int s = blockIdx.x; s < a.num_segments; s += gridDim.x) {
+        const int64_t so = a.segments[3 * (size_t)s], d_o = a.segments[3 * (size_t)s + 1], n = a.segments[3 * (size_t)s + 2];
+        const uint8_t* src = a.src + so;
+        uint8_t* dst = a.dst + d_o;
+        if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+            const int64_t n16 = n / 16;
+            for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<int4*>(dst)[i] = ld_stream(reinterpret_cast<const int4*>(src) + i);
+            for (int64_t i = n16 * 16 + threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+        } else {
+            for (int64_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+        }
+    }
+}
+
+cudaError_t launch_segmented_copy(const SegmentedCopyArgs& a, cudaStream_t stream) {
+    if (a.num_segments == 0) return cudaSuccess;
+    segmented_copy_kernel<<<a.num_segments < 1184 ? a.num_segments : 1184, 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace dx

@@ -74,7 +74,7 @@ extern "C" int dx_get_dispatch_layout_noalloc(const int64_t* topk_idx, int num_t
         cudaGetLastError();
         return fail(DX_NOALLOC_CUDA_ERROR, "cudaMemsetAsync failed (error %lld)", (long long)e);
     }
-    dx::LayoutArgs a;
+    dx::LayoutArgs a{};
     a.topk_idx = topk_idx;
     a.num_tokens = num_tokens;
     a.num_topk = num_topk;

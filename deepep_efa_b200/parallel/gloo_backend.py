@@ -18,6 +18,29 @@ from ..reference import oracle
 from ..utils.event import EventOverlap
 
 
+class _F8:
+    """An 8-bit float tensor as bytes: object collectives pickle tensors, and pickling knows no float8 storage."""
+
+    def __init__(self, t: torch.Tensor) -> None:
+        self.dtype, self.data = t.dtype, t.view(torch.uint8)
+
+
+def _encode(obj):
+    if isinstance(obj, torch.Tensor):
+        return _F8(obj) if obj.element_size() == 1 and obj.is_floating_point() else obj
+    if isinstance(obj, (tuple, list)):
+        return type(obj)(_encode(o) for o in obj)
+    return obj
+
+
+def _decode(obj):
+    if isinstance(obj, _F8):
+        return obj.data.view(obj.dtype)
+    if isinstance(obj, (tuple, list)):
+        return type(obj)(_decode(o) for o in obj)
+    return obj
+
+
 class GlooBackend:
     def __init__(self, rank: int, num_ranks: int, group) -> None:
         self.rank, self.num_ranks, self.group = rank, num_ranks, group
@@ -29,8 +52,8 @@ class GlooBackend:
         if self.num_ranks == 1:
             return [obj]
         out = [None] * self.num_ranks
-        dist.all_gather_object(out, obj, self.group)
-        return out
+        dist.all_gather_object(out, _encode(obj), self.group)
+        return [_decode(o) for o in out]
 
     def _masked(self):
         return tuple(int(i) for i in self.mask.nonzero().flatten().tolist())

@@ -111,8 +111,13 @@ def test_phase_profiler_accumulates_without_cuda():
     assert p.iters == 3  # without CUDA no events are recorded, but the bookkeeping must not fail
 
 
-def test_more_than_eight_ranks_is_a_documented_stub():
+def test_transport_stubs_and_domain_limits():
+    """The libfabric/EFA transport is a declared stub; a single-domain buffer refuses the cross-domain entry points."""
     import deepep_efa_b200 as ep
+    from deepep_efa_b200.parallel.transport import EfaTransport
+    with pytest.raises(NotImplementedError, match="libfabric"):
+        EfaTransport()
     fake_group = types.SimpleNamespace(rank=lambda: 0, size=lambda: 16)
-    with pytest.raises(NotImplementedError, match="NVSwitch"):
-        ep.Buffer(fake_group)
+    with pytest.raises(AssertionError, match="at most 8"):
+        ep.Buffer(fake_group, num_nvl_ranks=16)
+    assert ep.Buffer.get_dispatch_config(16) is not None and ep.Buffer.get_combine_config(64) is not None

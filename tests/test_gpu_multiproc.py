@@ -163,6 +163,135 @@ def _worker(rank, world, port, q):
         q.put((rank, traceback.format_exc()))
 
 
+def _worker_two_level(rank, world, port, q, P):
+    """The group as `world / P` NVLink domains of P GPUs: rail hops over NCCL, fan-out by the NVLink kernels."""
+    import traceback
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        torch.cuda.set_device(rank)
+        torch.set_num_threads(2)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import deepep_efa_b200 as ep
+        from deepep_efa_b200.reference import oracle
+        from helpers import make_routing, make_tokens
+
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+
+        def align():
+            torch.cuda.synchronize()
+            dist.barrier()
+
+        nodes = world // P
+        T, H, E, K = 200 + 8 * rank, 1024, 8 * world, 4
+        L = E // world
+        buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=128 << 20, explicitly_destroy=True, timeout_ms=20000, num_nvl_ranks=P)
+        assert buf.get_num_rdma_ranks() == nodes
+        x = make_tokens(T, H, "cuda", seed=rank)
+        idx, w = make_routing(T, E, K, "cuda", seed=rank, masked_fraction=0.05)
+        w = w.masked_fill(idx == -1, 0)
+        all_x, all_idx, all_w = [t.cpu() for t in gather(x.cpu())], [t.cpu() for t in gather(idx.cpu())], [t.cpu() for t in gather(w.cpu())]
+        flat = oracle.dispatch(all_x, all_idx, all_w, E)[rank]
+        rpm = flat["rank_prefix_matrix"]
+        order = [m * P + i for i in range(P) for m in range(nodes)]
+        rows = torch.cat([torch.arange(int(rpm[s - 1, rank]) if s else 0, int(rpm[s, rank])) for s in order])
+        ref = (x.float() * w.sum(dim=1, keepdim=True)).cpu()
+        for it in range(2):
+            align()
+            per_rank, per_node, per_expert, in_rank, _ = buf.get_dispatch_layout(idx, E)
+            o_rank, o_expert, o_in = oracle.get_dispatch_layout(all_idx[rank], E, world)
+            assert torch.equal(per_rank.cpu(), o_rank) and torch.equal(per_expert.cpu(), o_expert) and torch.equal(in_rank.cpu(), o_in)
+            assert per_node.tolist() == [int(o_in[:, n * P:(n + 1) * P].any(1).sum()) for n in range(nodes)]
+            align()
+            recv_x, recv_idx, recv_w, per_expert_list, handle, ev = buf.dispatch(
+                x, num_tokens_per_rank=per_rank, num_tokens_per_rdma_rank=per_node, is_token_in_rank=in_rank,
+                num_tokens_per_expert=per_expert, topk_idx=idx, topk_weights=w)
+            ev.current_stream_wait()
+            torch.cuda.synchronize()
+            buf.check_status()
+            assert torch.equal(recv_x.cpu(), flat["recv_x"][rows])
+            assert torch.equal(recv_idx.cpu(), flat["recv_topk_idx"][rows])
+            assert torch.equal(recv_w.cpu(), flat["recv_topk_weights"][rows])
+            assert per_expert_list == flat["num_recv_tokens_per_expert_list"]
+            assert handle[6].tolist() == rpm[:, rank].tolist()
+            y = torch.zeros_like(recv_x, dtype=torch.float32)
+            for e in range(L):
+                r_, k_ = (recv_idx == e).nonzero(as_tuple=True)
+                y[r_] += recv_x[r_].float() * recv_w[r_, k_].unsqueeze(1)
+            align()
+            combined, combined_w, _ = buf.combine(y.to(torch.bfloat16), handle, topk_weights=recv_w)
+            torch.cuda.synchronize()
+            buf.check_status()
+            assert oracle.calc_diff(ref, combined.float().cpu()) < 1e-4
+            assert (combined_w - w).abs().max() < 1e-6
+            align()
+            # cached handle with FP8 on both hops
+            (rq, rs), a, b, c, d, _ = buf.dispatch(x, handle=handle, quantize_fp8=True)
+            torch.cuda.synchronize()
+            wq, ws = oracle.per_token_cast_to_fp8(flat["recv_x"][rows])
+            assert a is None and torch.equal(rq.cpu().view(torch.uint8), wq.view(torch.uint8)) and torch.equal(rs.cpu(), ws)
+            # low latency across domains
+            align()
+            M = 256
+            want = oracle.low_latency_dispatch(all_x, all_idx, M, E, True)[rank]
+            (px, ps), cnt, ll_handle, _, _ = buf.low_latency_dispatch(x, idx, M, E, use_fp8=True)
+            torch.cuda.synchronize()
+            assert torch.equal(cnt.cpu(), want["packed_recv_count"]) and torch.equal(ll_handle[1].cpu(), want["layout_range"])
+            for le in range(L):
+                n = int(cnt[le])
+                assert torch.equal(ll_handle[0][le, :n].cpu(), want["src_info"][le, :n])
+                assert torch.equal(px[le, :n].cpu().view(torch.uint8), want["packed_recv_x"][le, :n].view(torch.uint8))
+                assert torch.equal(ps[le, :n].cpu(), want["packed_recv_x_scales"][le, :n])
+            sim = oracle.per_token_cast_back(px.view(-1, H).cpu(), ps.view(-1, H // 128).cpu()).view(px.shape).cuda()
+            align()
+            out, _, _ = buf.low_latency_combine(sim, idx, w, ll_handle)
+            torch.cuda.synchronize()
+            assert oracle.calc_diff(ref, out.float().cpu()) < 9e-4
+        buf.destroy()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+
+
+def _run_ranks(target, world, extra=()):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q) + tuple(extra)) for r in range(world)]
+    for p in procs:
+        p.start()
+    import queue as _queue
+    import time
+    res, deadline = [], time.time() + 420
+    while len(res) < world and time.time() < deadline:
+        try:
+            res.append(q.get(timeout=5))
+        except _queue.Empty:
+            if res and any(m != "ok" for _, m in res):
+                break
+    for p in procs:
+        p.join(5)
+        if p.is_alive():
+            p.terminate()
+    for rank, msg in res:
+        assert msg == "ok", f"rank {rank}: {msg}"
+    assert len(res) == world, f"only {len(res)} of {world} ranks reported"
+
+
+@pytest.mark.parametrize("world,P", [(2, 1), (4, 2)])
+def test_two_level_path_multiprocess(world, P):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run_ranks(_worker_two_level, world, (P,))
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_multiprocess_against_oracle(world):
     if torch.cuda.device_count() < world:

@@ -83,6 +83,7 @@ def main(args) -> None:
         buf.low_latency_combine(sim, topk_idx, topk_w, handle)
 
     try:
+        B.ramp_clocks(local_rank)
         sampler = B.ClockSampler() if rank == 0 else None
         if sampler is not None:
             sampler.start()

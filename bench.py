@@ -106,6 +106,47 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+def ramp_clocks(local_rank: int, max_seconds: float = 12.0) -> None:
+    """Untimed: keep the SMs busy with a light streaming kernel until the SM clock reads (nearly) its maximum.
+
+    An idle GPU sits at its lowest clock and some machines take several seconds to ramp up; a latency benchmark that
+    starts before that measures the ramp, not the kernels. Clocks are only read (NVML), never set."""
+    import time
+    buf = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    handle = nvml = None
+    try:
+        import pynvml as nvml
+        nvml.nvmlInit()
+        handle = nvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(local_rank))
+        top = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+    except Exception:
+        handle = None
+    t0, last = time.time(), None
+    while time.time() - t0 < max_seconds:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(40):
+            buf.add_(1.0)
+        e.record()
+        torch.cuda.synchronize()
+        if handle is not None:
+            try:
+                if nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM) >= 0.93 * top:
+                    break
+                continue
+            except Exception:
+                handle = None
+        ms = s.elapsed_time(e)  # no NVML: stop when the same work stops getting faster
+        if last is not None and ms > 0.97 * last and time.time() - t0 > 1.0:
+            break
+        last = ms
+    if nvml is not None:
+        try:
+            nvml.nvmlShutdown()
+        except Exception:
+            pass
+
+
 # ------------------------------------------------------------------------------------------------
 # helpers
 # ------------------------------------------------------------------------------------------------
@@ -190,6 +231,7 @@ def run_ours(args):
 
     # one sampler (rank 0) for all GPUs of the job; it runs from the warm-up through both timed regions (device-timed and
     # end-to-end), which execute the same workload back to back
+    ramp_clocks(local_rank)
     sampler = ClockSampler() if rank == 0 else None
     if sampler is not None:
         sampler.start()

@@ -26,7 +26,7 @@ import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-from bench import init_dist, max_over_ranks  # noqa: E402
+from bench import init_dist, max_over_ranks, ramp_clocks  # noqa: E402
 
 
 def zipf_routing(tokens, num_experts, topk, s, gen):
@@ -56,7 +56,8 @@ def run(args):
     import deepep_efa_b200 as ep
     from deepep_efa_b200.models.moe import MoEConfig, MoELayer
 
-    rank, world, _ = init_dist(args.gpus)
+    rank, world, local_rank = init_dist(args.gpus)
+    ramp_clocks(local_rank)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))

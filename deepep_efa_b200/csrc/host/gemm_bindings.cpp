@@ -41,6 +41,20 @@ int sm_count(int device) {
     return n;
 }
 
+// SM clock in kHz, cached: this attribute query goes to the driver and costs about a millisecond per call.
+int clock_khz(int device) {
+    static std::mutex mu;
+    static std::map<int, int> cache;
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(device);
+    if (it != cache.end()) return it->second;
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device);
+    if (khz <= 0) khz = 1965000;
+    cache[device] = khz;
+    return khz;
+}
+
 // mode 0: a [M,K], b [G,N,K] (or [G*N,K]), m_offsets [G+1] -> c [M, N] (or [M, N/2] with swiglu)
 // mode 1: a [N_out, M], b [K_out, M], m_offsets [G+1] -> c [G, N_out, K_out]
 torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& m_offsets, int mode, bool swiglu,
@@ -108,9 +122,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         p.tile_order = (o != nullptr && o[0] == '1') ? 1 : 0;
     }
     p.error_flag = error_flag(device).data_ptr<int>();
-    int khz = 0;
-    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device);
-    p.timeout_cycles = (long long)(timeout_ms * (double)(khz > 0 ? khz : 1965000));
+    p.timeout_cycles = (long long)(timeout_ms * (double)clock_khz(device));
     const cudaError_t e = dx::launch_grouped_gemm(p, at::cuda::getCurrentCUDAStream(device).stream());
     if (e == cudaErrorInvalidValue) {
         cudaGetLastError();

@@ -598,8 +598,14 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
     }
     if (!ok) return cudaErrorInvalidValue;
     auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
-    if (e != cudaSuccess) return e;
+    static bool smem_opted_in[64] = {};  // per device, once: the attribute is sticky
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !smem_opted_in[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) smem_opted_in[dev] = true;
+    }
     kernel<<<a.num_sms, C::kThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
     return cudaGetLastError();
 }

@@ -623,6 +623,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("query_mask", &Runtime::query_mask)
         .def("clean_mask", &Runtime::clean_mask)
         .def("set_timeout_ms", [](Runtime& r, double ms) { r.core->set_timeout_ms(ms); })
+        .def("set_debug_checks", [](Runtime& r, bool on) { r.core->set_debug_checks(on); })
+        .def("debug_checks", [](Runtime& r) { return r.core->debug_checks(); })
         .def("timeout_ms", [](Runtime& r) { return r.core->timeout_ms(); })
         .def("status_code", [](Runtime& r) { return r.core->status_code(); })
         .def("status_string", [](Runtime& r) { return r.core->status_string(); })

@@ -54,6 +54,7 @@ inline const char* status_name(int code) {
         case dx::kTimeoutGemm: return "timeout inside grouped GEMM pipeline";
         case dx::kBadArgument: return "kernel rejected its arguments";
         case dx::kTimeoutTest: return "timeout probe (expected in tests)";
+        case dx::kBadPeerAccess: return "debug bounds check: a row address fell outside the peer's symmetric buffer (access skipped)";
         default: return "unknown status";
     }
 }
@@ -98,12 +99,16 @@ class RuntimeCore {
         DX_CUDA_CHECK(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device_));
         clock_khz_ = khz > 0 ? khz : 1965000;
         set_timeout_ms(timeout_ms);
+        if (const char* e = std::getenv("DEEPEP_DEBUG_CHECKS"); e != nullptr && e[0] == '1') debug_checks_ = true;
         for (int i = 0; i < dx::kMaxRanks; ++i) peers_[i] = nullptr;
         peers_[rank_] = base_;
         DX_CUDA_CHECK(cudaDeviceSynchronize());
     }
 
     ~RuntimeCore() { release(); }
+
+    void set_debug_checks(bool on) { debug_checks_ = on; }
+    bool debug_checks() const { return debug_checks_; }
 
     void set_timeout_ms(double ms) {
         timeout_ms_ = ms;
@@ -171,6 +176,7 @@ class RuntimeCore {
         c.trace = trace_;
         c.timeout_cycles = timeout_cycles_;
         c.mask_on_timeout = mask_on_timeout_ ? 1 : 0;
+        c.debug_extent = debug_checks_ ? (unsigned long long)total_bytes_ : 0ull;
         return c;
     }
 
@@ -349,6 +355,7 @@ class RuntimeCore {
 
     int rank_, num_ranks_, device_;
     bool mask_on_timeout_ = false;
+    bool debug_checks_ = false;  // range-check row addresses on the device (env DEEPEP_DEBUG_CHECKS=1 or set_debug_checks)
     bool available_ = false, released_ = false;
     void* base_ = nullptr;
     uint64_t total_bytes_ = 0, ll_base_ = 0, ll_bytes_ = 0;

@@ -199,7 +199,10 @@ __global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid
                 for (int src = 0; src < me; ++src)
                     if (!s_mask[src]) begin += __ldcg(&my_counts[(size_t)src * E + e]);
                 const int row = begin + s_row[tid];
-                if (row >= N || s_mask[s_dst_rank[tid]]) s_row[tid] = -1;  // row >= N cannot happen with a consistent max_tokens
+                const size_t row_bytes = (size_t)H * (a.use_fp8 ? 1 : 2);
+                if (row >= N || s_mask[s_dst_rank[tid]] ||
+                    !peer_range_ok(c, s_dst_rank[tid], c.at<char>(s_dst_rank[tid], a.region.recv_x_off[P]) + ((size_t)s_dst_le[tid] * N + (row < N ? row : 0)) * row_bytes, row_bytes, 3))
+                    s_row[tid] = -1;  // row >= N cannot happen with a consistent max_tokens
                 else {
                     s_row[tid] = row;
                     atomicAdd(&s_sent[s_dst_rank[tid]], 1);
@@ -394,6 +397,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_
             if (token < 0 || token >= M) continue;
             const int4* from = reinterpret_cast<const int4*>(a.x) + ((size_t)le * N + n) * n16;
             int4* to = reinterpret_cast<int4*>(c.at<char>(src, a.region.combine_stage_off[P])) + ((size_t)(me * L + le) * M + token) * n16;
+            if (!peer_range_ok(c, src, to, (size_t)n16 * 16, 4)) continue;
             const int lo16 = part * half16, hi16 = min(n16, lo16 + half16);
             constexpr int U = 14;
             for (int i0 = lo16; i0 < hi16; i0 += 32 * U) {

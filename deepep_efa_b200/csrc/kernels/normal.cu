@@ -223,6 +223,10 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const __g
         for (int d = 0; d < kMaxRanks; ++d) {
             const int h = __shfl_sync(0xffffffffu, head, d);
             rows[d] = (d < R && h >= 0) ? s_dst[d].base_row + h : -1;
+            if (c.debug_extent != 0 && rows[d] >= 0 &&
+                !peer_range_ok(c, d, s_dst[d].x + (size_t)rows[d] * ((size_t)a.hidden * (a.quantize != 0 ? 1 : a.x_elem_bytes)),
+                               (size_t)a.hidden * (a.quantize != 0 ? 1 : a.x_elem_bytes), 1))
+                rows[d] = -1;
         }
 
         if (!quant) {
@@ -383,7 +387,8 @@ __device__ __forceinline__ void combine_rows(const CombineArgs& a, const PeerSrc
             const int h = __shfl_sync(0xffffffffu, head, r);
             const bool ok = r < R && h >= 0;
             rowp[r] = ok ? s_src[r].x + (size_t)(s_src[r].base_row + h) * n16 : nullptr;
-            wp[r] = (ok && s_src[r].w != nullptr) ? s_src[r].w + (size_t)(s_src[r].base_row + h) * K : nullptr;
+            if (a.ctx.debug_extent != 0 && ok && !peer_range_ok(a.ctx, r, rowp[r], (size_t)n16 * 16, 2)) rowp[r] = nullptr;
+            wp[r] = (ok && rowp[r] != nullptr && s_src[r].w != nullptr) ? s_src[r].w + (size_t)(s_src[r].base_row + h) * K : nullptr;
         }
         const int4* b0 = a.bias0 ? reinterpret_cast<const int4*>(a.bias0) + (size_t)t * n16 : nullptr;
         const int4* b1 = a.bias1 ? reinterpret_cast<const int4*>(a.bias1) + (size_t)t * n16 : nullptr;

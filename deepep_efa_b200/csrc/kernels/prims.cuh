@@ -104,6 +104,18 @@ __device__ __forceinline__ void report(StatusBlock* sb, int code, int rank, int 
 
 // Spins on `*flag >= want` (acquire, system scope) for at most `limit` clock cycles.
 // Returns true when the value arrived.
+// Debug aid (RankCtx::debug_extent != 0, env DEEPEP_DEBUG_CHECKS=1): is [p, p+bytes) inside rank r's symmetric buffer?
+// A violation is reported through the status block and the caller skips the access, so a corrupted handle or a wrong
+// size shows up as an error code on the host instead of as a fault on a peer's GPU.
+__device__ __forceinline__ bool peer_range_ok(const RankCtx& c, int r, const void* p, size_t bytes, int detail) {
+    if (c.debug_extent == 0) return true;
+    const char* base = reinterpret_cast<const char*>(c.peers[r]);
+    const char* q = reinterpret_cast<const char*>(p);
+    if (q >= base && q + bytes <= base + c.debug_extent) return true;
+    report(c.status, kBadPeerAccess, c.rank, r, detail);
+    return false;
+}
+
 __device__ __forceinline__ bool wait_ge_sys(const uint64_t* flag, uint64_t want, long long limit) {
     if (ld_acquire_sys(flag) >= want) return true;
     const long long t0 = clock64();

@@ -24,6 +24,7 @@ enum Status : int {
     kTimeoutGemm = 8,
     kBadArgument = 9,
     kTimeoutTest = 10,
+    kBadPeerAccess = 11,  // debug bounds check: a row address fell outside the peer's symmetric buffer (access skipped)
 };
 
 // Written by kernels into mapped pinned host memory; read by the host after collective calls.
@@ -90,6 +91,7 @@ struct RankCtx {
     unsigned long long* trace;   // optional device buffer for phase time stamps (nullptr = tracing off)
     long long timeout_cycles;
     int mask_on_timeout;         // low-latency shrink mode: a rank that times out is masked instead of failing the call
+    unsigned long long debug_extent;  // 0 = off; else bytes of every rank's symmetric buffer: row addresses are range-checked
 
 #ifdef __CUDACC__
     __device__ __forceinline__ ControlBlock* ctrl(int r) const { return reinterpret_cast<ControlBlock*>(peers[r]); }

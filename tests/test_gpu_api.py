@@ -94,10 +94,10 @@ def test_int32_expert_ids_and_accessors(buf):
     assert buf.get_local_device_id() == torch.cuda.current_device()
     assert len(buf.get_local_ipc_handle()) == 64
     assert buf.get_comm_stream() is buf.comm_stream
+    with pytest.raises(NotImplementedError):  # a single NVLink domain has no cross-domain path
+        buf.internode_dispatch(torch.empty(0))
     with pytest.raises(NotImplementedError):
-        buf.internode_dispatch()
-    with pytest.raises(NotImplementedError):
-        buf.internode_combine()
+        buf.internode_combine(torch.empty(0), ())
 
 
 def test_low_latency_repeated_runs_hash_identical(buf):

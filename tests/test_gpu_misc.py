@@ -46,6 +46,41 @@ def test_timed_out_wait_reports_status_and_context_survives():
         vc.destroy()
 
 
+def test_debug_range_check_turns_a_bad_row_into_a_status():
+    """With the debug range checks on, a cached handle whose send position points far outside the symmetric buffer
+    makes the kernel skip that row and report a status code; everything else of the call still happens."""
+    from deepep_efa_b200 import EPTimeoutError
+    from deepep_efa_b200.parallel.virtual import VirtualCluster
+    from helpers import make_routing, make_tokens
+    vc = VirtualCluster(1, num_nvl_bytes=32 << 20)
+    try:
+        b = vc.buffers[0]
+        b.runtime.set_debug_checks(True)
+        T, H, E, K = 64, 512, 8, 2
+        x = make_tokens(T, H, "cuda", seed=1)
+        idx, w = make_routing(T, E, K, "cuda", seed=1)
+        per_rank, _, per_expert, in_rank, _ = b.get_dispatch_layout(idx, E)
+        recv_x, _, _, _, handle, _ = b.dispatch(x, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank,
+                                                num_tokens_per_expert=per_expert, topk_idx=idx, topk_weights=w)
+        b.check_status(sync=True)  # the checks do not fire on a healthy call
+        assert torch.equal(recv_x, x)
+        bad_head = handle[5].clone()
+        bad_head[5, 0] = 1 << 27  # row 2^27 of a 1 KiB row: a terabyte past the buffer
+        bad = handle[:5] + (bad_head,)
+        rx2, *_ = b.dispatch(x, handle=bad)
+        with pytest.raises(EPTimeoutError) as ei:
+            b.check_status(sync=True)
+        assert "bounds check" in str(ei.value)
+        keep = torch.arange(T, device="cuda") != 5
+        assert torch.equal(rx2[keep], x[keep])
+        b.recover()
+        rx3, *_ = b.dispatch(x, handle=handle)
+        b.check_status(sync=True)
+        assert torch.equal(rx3, x)
+    finally:
+        vc.destroy()
+
+
 def test_symmetric_alloc_and_views():
     from deepep_efa_b200.parallel.virtual import VirtualCluster
     vc = VirtualCluster(1, num_nvl_bytes=16 << 20)

@@ -34,6 +34,7 @@ CUDA_SOURCES = [
     "kernels/permute.cu",
     "kernels/noalloc.cu",
     "kernels/hier.cu",
+    "kernels/train_ops.cu",
 ]
 CPP_SOURCES = [
     "host/bindings.cpp",

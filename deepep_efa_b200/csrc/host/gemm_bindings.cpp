@@ -199,7 +199,53 @@ void gemm_clear_error(int device) { error_flag(device).zero_(); }
 
 }  // namespace
 
+torch::Tensor transpose_bf16(const torch::Tensor& x) {
+    DXG_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == torch::kBFloat16 && (x.dim() == 2 || x.dim() == 3), "transpose_bf16: contiguous CUDA bf16 [R,C] or [B,R,C]");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t B = x.dim() == 3 ? x.size(0) : 1, R = x.size(-2), C = x.size(-1);
+    auto out = x.dim() == 3 ? torch::empty({B, C, R}, x.options()) : torch::empty({C, R}, x.options());
+    const cudaError_t e = dx::launch_transpose_bf16(x.data_ptr(), out.data_ptr(), (int)B, (int)R, (int)C, at::cuda::getCurrentCUDAStream(x.get_device()).stream());
+    DXG_CHECK(e == cudaSuccess, "transpose_bf16: rows and cols must be multiples of 8");
+    return out;
+}
+
+torch::Tensor swiglu_fwd(const torch::Tensor& h13) {
+    DXG_CHECK(h13.is_cuda() && h13.is_contiguous() && h13.scalar_type() == torch::kBFloat16 && h13.dim() == 2 && h13.size(1) % 16 == 0, "swiglu_fwd: contiguous CUDA bf16 [M, 2*I], I % 8 == 0");
+    c10::cuda::CUDAGuard guard(h13.device());
+    const int inter = (int)(h13.size(1) / 2);
+    auto h = torch::empty({h13.size(0), inter}, h13.options());
+    const cudaError_t e = dx::launch_swiglu_fwd(h13.data_ptr(), h.data_ptr(), h13.size(0), inter, at::cuda::getCurrentCUDAStream(h13.get_device()).stream());
+    DXG_CHECK(e == cudaSuccess, "swiglu_fwd launch failed");
+    return h;
+}
+
+torch::Tensor swiglu_bwd(const torch::Tensor& h13, const torch::Tensor& dh) {
+    DXG_CHECK(h13.is_cuda() && h13.is_contiguous() && h13.scalar_type() == torch::kBFloat16 && h13.dim() == 2 && h13.size(1) % 16 == 0, "swiglu_bwd: contiguous CUDA bf16 [M, 2*I]");
+    DXG_CHECK(dh.is_cuda() && dh.is_contiguous() && dh.scalar_type() == torch::kBFloat16 && dh.dim() == 2 && dh.size(0) == h13.size(0) && dh.size(1) * 2 == h13.size(1), "swiglu_bwd: dh must be bf16 [M, I]");
+    c10::cuda::CUDAGuard guard(h13.device());
+    auto out = torch::empty_like(h13);
+    const cudaError_t e = dx::launch_swiglu_bwd(h13.data_ptr(), dh.data_ptr(), out.data_ptr(), h13.size(0), (int)dh.size(1), at::cuda::getCurrentCUDAStream(h13.get_device()).stream());
+    DXG_CHECK(e == cudaSuccess, "swiglu_bwd launch failed");
+    return out;
+}
+
+torch::Tensor rowdot(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& pos) {
+    DXG_CHECK(a.is_cuda() && a.is_contiguous() && a.scalar_type() == torch::kBFloat16 && a.dim() == 2, "rowdot: a must be contiguous CUDA bf16 [M,H]");
+    DXG_CHECK(b.is_cuda() && b.is_contiguous() && b.scalar_type() == torch::kBFloat16 && b.dim() == 2 && b.size(1) == a.size(1), "rowdot: b must be bf16 [N,H]");
+    DXG_CHECK(pos.is_cuda() && pos.is_contiguous() && pos.scalar_type() == torch::kInt32 && pos.dim() == 2 && pos.size(0) == b.size(0), "rowdot: pos must be int32 [N,K]");
+    c10::cuda::CUDAGuard guard(a.device());
+    auto out = torch::empty({pos.size(0), pos.size(1)}, a.options().dtype(torch::kFloat32));
+    const cudaError_t e = dx::launch_rowdot(a.data_ptr(), b.data_ptr(), pos.data_ptr<int>(), out.data_ptr<float>(), (int)pos.size(0), (int)pos.size(1), (int)a.size(1),
+                                            at::cuda::getCurrentCUDAStream(a.get_device()).stream());
+    DXG_CHECK(e == cudaSuccess, "rowdot: hidden must be a multiple of 8");
+    return out;
+}
+
 void bind_gemm(py::module_& m) {
+    m.def("transpose_bf16", &transpose_bf16);
+    m.def("swiglu_fwd", &swiglu_fwd);
+    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("rowdot", &rowdot);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
           py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none());

@@ -58,4 +58,14 @@ cudaError_t launch_gather_rows(const void* src, void* dst, const int* src_row, c
 cudaError_t launch_gather_reduce_rows(const void* src, void* dst, const int* pos, const float* w, int num_dst_rows, int num_k, int hidden,
                                       cudaStream_t stream);
 
+// Training-step helpers (train_ops.cu). All tensors bf16 unless noted.
+//   out[b, c, r] = in[b, r, c]                     rows and cols multiples of 8
+cudaError_t launch_transpose_bf16(const void* in, void* out, int batch, int rows, int cols, cudaStream_t stream);
+//   h[m, i] = silu(h13[m, i]) * h13[m, inter + i]
+cudaError_t launch_swiglu_fwd(const void* h13, void* h, long long rows, int inter, cudaStream_t stream);
+//   dh13 = d/dh13 of the above given dh
+cudaError_t launch_swiglu_bwd(const void* h13, const void* dh, void* dh13, long long rows, int inter, cudaStream_t stream);
+//   out[n, k] = <a[pos[n, k]], b[n]>  (f32 out, 0 where pos < 0)
+cudaError_t launch_rowdot(const void* a, const void* b, const int* pos, float* out, int n_rows, int num_k, int hidden, cudaStream_t stream);
+
 }  // namespace dx

@@ -90,8 +90,8 @@ class _GroupedLinear(torch.autograd.Function):
         x, w, m_offsets = ctx.saved_tensors
         grad = grad.contiguous()
         if x.is_cuda:
-            dx = gg.grouped_gemm(grad, w.transpose(1, 2).contiguous(), m_offsets)
-            dw = gg.grouped_gemm_wgrad(grad.t().contiguous(), x.t().contiguous(), m_offsets)
+            dx = gg.grouped_gemm(grad, gg.transpose_last2(w), m_offsets)
+            dw = gg.grouped_gemm_wgrad(gg.transpose_last2(grad), gg.transpose_last2(x), m_offsets)
         else:
             dx = gg.reference_grouped_gemm(grad, w.transpose(1, 2).contiguous(), m_offsets).to(x.dtype)
             offs = m_offsets.tolist()
@@ -143,8 +143,7 @@ class MoELayer(nn.Module):
         plan = build_expert_plan(routing["recv_topk_idx"], routing["counts"])
         x_perm = permute(recv_x, plan)
         h13 = grouped_linear(x_perm, self.w13, plan.m_offsets)
-        inter = self.cfg.intermediate
-        h = F.silu(h13[:, :inter].float()).mul(h13[:, inter:].float()).to(torch.bfloat16)
+        h = gg.swiglu(h13)
         y_perm = grouped_linear(h, self.w2, plan.m_offsets)
         out_buf = self._symmetric_like(recv_x)
         y_recv = unpermute_weighted(y_perm, recv_w, plan, out_buf)

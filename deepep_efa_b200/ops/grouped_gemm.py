@@ -61,3 +61,36 @@ def reference_grouped_gemm(a: torch.Tensor, b: torch.Tensor, m_offsets: torch.Te
             y = torch.nn.functional.silu(gate) * up
         out[r] = y
     return out
+
+
+def transpose_last2(x: torch.Tensor) -> torch.Tensor:
+    """Contiguous ``x.transpose(-1, -2)`` for a 2-D or 3-D tensor (tiled kernel for bf16 on the GPU)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() in (2, 3) and x.size(-1) % 8 == 0 and x.size(-2) % 8 == 0:
+        return _ext.load().transpose_bf16(x.contiguous())
+    return x.transpose(-1, -2).contiguous()
+
+
+class _SwiGLU(torch.autograd.Function):
+    """``h = silu(h13[:, :I]) * h13[:, I:]`` with fp32 math and bf16 storage, one kernel per direction."""
+
+    @staticmethod
+    def forward(ctx, h13):
+        ctx.save_for_backward(h13)
+        if h13.is_cuda and h13.dtype == torch.bfloat16 and h13.size(1) % 16 == 0:
+            return _ext.load().swiglu_fwd(h13.contiguous())
+        inter = h13.size(1) // 2
+        return (torch.nn.functional.silu(h13[:, :inter].float()) * h13[:, inter:].float()).to(h13.dtype)
+
+    @staticmethod
+    def backward(ctx, dh):
+        (h13,) = ctx.saved_tensors
+        if h13.is_cuda and h13.dtype == torch.bfloat16 and h13.size(1) % 16 == 0:
+            return _ext.load().swiglu_bwd(h13.contiguous(), dh.contiguous().to(torch.bfloat16))
+        inter = h13.size(1) // 2
+        g, u, d = h13[:, :inter].float(), h13[:, inter:].float(), dh.float()
+        sig = torch.sigmoid(g)
+        return torch.cat([d * u * sig * (1 + g * (1 - sig)), d * g * sig], dim=1).to(h13.dtype)
+
+
+def swiglu(h13: torch.Tensor) -> torch.Tensor:
+    return _SwiGLU.apply(h13)

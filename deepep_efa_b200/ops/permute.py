@@ -124,6 +124,8 @@ class _UnpermuteWeighted(torch.autograd.Function):
         row_scale = torch.where(plan.src_row >= 0, w_flat[idx], torch.zeros_like(w_flat[idx])).float().contiguous()
         d_y_perm = gather_rows(grad, plan.src_row, row_scale)
         # d w[n, k] = <y_perm[pos[n, k]], grad[n]>
+        if grad.is_cuda and grad.dtype == torch.bfloat16 and y_perm.dtype == torch.bfloat16:
+            return d_y_perm, _ext.load().rowdot(y_perm, grad, plan.pos).to(weights.dtype), None, None
         d_w = torch.zeros_like(weights)
         for k in range(K):
             p = plan.pos[:, k]

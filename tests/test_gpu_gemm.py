@@ -131,3 +131,38 @@ def test_bf16_wgrad_kgrouped():
             assert dw[g].float().abs().max().item() == 0
         else:
             assert _rel_err(dw[g], ref) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(64, 64), (200, 72), (3, 136, 4096), (2, 1408, 264)])
+def test_transpose_kernel(shape):
+    from deepep_efa_b200.ops.grouped_gemm import transpose_last2
+    torch.manual_seed(7)
+    x = torch.randn(*shape, device="cuda").to(torch.bfloat16)
+    assert torch.equal(transpose_last2(x), x.transpose(-1, -2).contiguous())
+
+
+def test_swiglu_kernels_match_autograd():
+    from deepep_efa_b200.ops.grouped_gemm import swiglu
+    torch.manual_seed(8)
+    M, I = 300, 1408
+    h13 = torch.randn(M, 2 * I, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    dh = torch.randn(M, I, device="cuda").to(torch.bfloat16)
+    h = swiglu(h13)
+    h.backward(dh)
+    ref_in = h13.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.silu(ref_in[:, :I]) * ref_in[:, I:]
+    ref.backward(dh.float())
+    assert _rel_err(h, ref.detach()) < 4e-3
+    assert _rel_err(h13.grad, ref_in.grad) < 4e-3
+
+
+def test_rowdot_kernel():
+    from deepep_efa_b200 import _ext
+    torch.manual_seed(9)
+    Mp, N, K, H = 500, 120, 6, 4096
+    a = torch.randn(Mp, H, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, H, device="cuda").to(torch.bfloat16)
+    pos = torch.randint(-1, Mp, (N, K), device="cuda", dtype=torch.int32)
+    got = _ext.load().rowdot(a, b, pos)
+    want = torch.where(pos >= 0, (a[pos.clamp(min=0).long()].float() * b.float().unsqueeze(1)).sum(-1), torch.zeros(N, K, device="cuda"))
+    assert torch.allclose(got, want, rtol=1e-3, atol=1e-2)

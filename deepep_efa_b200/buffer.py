@@ -735,6 +735,9 @@ def _dispatch_many(bufs: List[Buffer], reqs: List[_DispatchReq], config: Config,
         per_rank, outs_all = [], []
         for b, q, (rpm, cpm, rcpm, send_head, itir, n_recv, per_expert) in zip(bufs, reqs, metas):
             x, x_scales = q.x if isinstance(q.x, tuple) else (q.x, None)
+            x = x.contiguous()
+            if x_scales is not None:
+                x_scales = x_scales.contiguous()  # the reference's tests pass column-major scales (tests/test_intranode.py:29)
             H = x.size(1)
             rt = b.runtime
             quant = q.quantize_fp8

@@ -89,8 +89,11 @@ __device__ __forceinline__ QuantChunk quantize_chunk(const char* row, int ch, bo
 // =============================================================================================
 // dispatch
 // =============================================================================================
+// The kernels are named dx::ll::dispatch and dx::ll::combine: tools written for the reference and for upstream DeepEP
+// (tests/utils.py:173-271) find the low-latency kernels in a profiler trace by the substrings "::dispatch" / "::combine".
+namespace ll {
 template <int V>
-__global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid_constant__ ArgPack<LLDispatchArgs, V> pack) {
+__global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant__ ArgPack<LLDispatchArgs, V> pack) {
     pdl_wait_predecessor();
     pdl_release_successor();
     const LLDispatchArgs& a = pack.a[blockIdx.y];
@@ -312,16 +315,19 @@ __global__ void __launch_bounds__(kLLThreads, 1) ll_dispatch_kernel(const __grid
     }
 }
 
+}  // namespace ll
+
 cudaError_t launch_ll_dispatch(const LLDispatchArgs* a, int nv, cudaStream_t stream) {
     const size_t smem = ((size_t)a[0].num_tokens * a[0].num_topk + a[0].num_experts) * sizeof(int);
-    return DX_LAUNCH_RANKED_PDL(ll_dispatch_kernel, LLDispatchArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
+    return DX_LAUNCH_RANKED_PDL(ll::dispatch, LLDispatchArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
 }
 
 // =============================================================================================
 // combine
 // =============================================================================================
+namespace ll {
 template <int V>
-__global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_constant__ ArgPack<LLCombineArgs, V> pack) {
+__global__ void __launch_bounds__(kLLThreads, 1) combine(const __grid_constant__ ArgPack<LLCombineArgs, V> pack) {
     pdl_wait_predecessor();
     pdl_release_successor();
     const LLCombineArgs& a = pack.a[blockIdx.y];
@@ -520,9 +526,11 @@ __global__ void __launch_bounds__(kLLThreads, 1) ll_combine_kernel(const __grid_
     }
 }
 
+}  // namespace ll
+
 cudaError_t launch_ll_combine(const LLCombineArgs* a, int nv, cudaStream_t stream) {
     const size_t smem = ((size_t)a[0].num_experts / a[0].ctx.num_ranks + 1) * sizeof(int);
-    return DX_LAUNCH_RANKED_PDL(ll_combine_kernel, LLCombineArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
+    return DX_LAUNCH_RANKED_PDL(ll::combine, LLCombineArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
 }
 
 }  // namespace dx

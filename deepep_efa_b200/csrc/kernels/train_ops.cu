@@ -19,29 +19,32 @@ namespace {
 constexpr int kTile = 64;
 
 __global__ void __launch_bounds__(256) transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int C) {
-    // one padded row per tile row: 64 bf16 + 8 of padding keeps the 16-byte row starts aligned and spreads the banks
-    __shared__ __align__(16) __nv_bfloat16 tile[kTile][kTile + 8];
+    // 64x64 tile without padding; the 16-byte chunk `ch` of row r lives at chunk position ch ^ ((r >> 3) & 7). Rows that are a
+    // multiple of 8 apart (what the lanes of the store phase read together) then sit in different banks, and the 8 lanes
+    // that fill one row in the load phase still cover it exactly once.
+    __shared__ __align__(16) __nv_bfloat16 tile[kTile][kTile];
     const size_t plane = (size_t)R * C;
     const __nv_bfloat16* src = in + blockIdx.z * plane;
     __nv_bfloat16* dst = out + blockIdx.z * plane;
     const int r0 = blockIdx.y * kTile, c0 = blockIdx.x * kTile;
     const int tid = threadIdx.x;
-    // load: 64 rows x 8 chunks of 8 elements
     for (int i = tid; i < kTile * 8; i += 256) {
-        const int r = i >> 3, ch = (i & 7) * 8;
+        const int r = i >> 3, ch = i & 7;
         int4 v = make_int4(0, 0, 0, 0);
-        if (r0 + r < R && c0 + ch < C) v = *reinterpret_cast<const int4*>(src + (size_t)(r0 + r) * C + c0 + ch);
-        *reinterpret_cast<int4*>(&tile[r][ch]) = v;
+        if (r0 + r < R && c0 + ch * 8 < C) v = *reinterpret_cast<const int4*>(src + (size_t)(r0 + r) * C + c0 + ch * 8);
+        *reinterpret_cast<int4*>(&tile[r][(ch ^ ((r >> 3) & 7)) * 8]) = v;
     }
     __syncthreads();
-    // store: output row = input column; 8 consecutive input rows make one 16-byte chunk
+    // store: output row = input column c; lane (i & 7) = q assembles input rows 8q..8q+7 into one 16-byte chunk, so 8
+    // consecutive lanes write one full 128-byte output row segment
     for (int i = tid; i < kTile * 8; i += 256) {
-        const int c = i >> 3, rch = (i & 7) * 8;
-        if (c0 + c >= C || r0 + rch >= R) continue;
+        const int c = i >> 3, q = i & 7;
+        if (c0 + c >= C || r0 + q * 8 >= R) continue;
+        const int col = (((c >> 3) ^ q) << 3) + (c & 7);  // (r >> 3) & 7 == q for the rows 8q..8q+7
         __align__(16) __nv_bfloat16 v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = tile[rch + j][c];
-        *reinterpret_cast<int4*>(dst + (size_t)(c0 + c) * R + r0 + rch) = *reinterpret_cast<const int4*>(v);
+        for (int j = 0; j < 8; ++j) v[j] = tile[q * 8 + j][col];
+        *reinterpret_cast<int4*>(dst + (size_t)(c0 + c) * R + r0 + q * 8) = *reinterpret_cast<const int4*>(v);
     }
 }
 

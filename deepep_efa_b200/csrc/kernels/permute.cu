@@ -73,31 +73,53 @@ __global__ void __launch_bounds__(kPermThreads) gather_reduce_rows_kernel(const 
         my_pos = pos[(size_t)n * num_k + lane];
         my_w = w != nullptr ? w[(size_t)n * num_k + lane] : 1.f;
     }
-    const unsigned valid = __ballot_sync(0xffffffffu, my_pos >= 0);
+    unsigned valid = __ballot_sync(0xffffffffu, my_pos >= 0);
     int4* d = reinterpret_cast<int4*>(dst) + (size_t)n * n16;
-    for (int i = lane; i < n16; i += 32) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        unsigned rest = valid;
-        while (rest) {
-            const int k = __ffs(rest) - 1;
-            rest &= rest - 1;
-            const int p = __shfl_sync(0xffffffffu, my_pos, k);
-            const float wk = __shfl_sync(0xffffffffu, my_w, k);
-            const int4 v = ld_stream(reinterpret_cast<const int4*>(src) + (size_t)p * n16 + i);
-            const uint32_t u[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+    // Selections compacted onto the low lanes; a row at an expert rank typically has one or two valid selections, so the
+    // memory-level parallelism comes from four column chunks per lane being in flight at once.
+    const int nv = __popc(valid);
+    const int from = lane < nv ? __fns(valid, 0, lane + 1) : 0;
+    const int pos_c = __shfl_sync(0xffffffffu, my_pos, from);
+    const float w_c = __shfl_sync(0xffffffffu, my_w, from);
+    constexpr int U = 4;
+    for (int i0 = 0; i0 < n16; i0 += 32 * U) {
+        float acc[U][8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = bf16x2_to_f2(u[j]);
-                acc[2 * j] = fmaf(wk, f.x, acc[2 * j]);
-                acc[2 * j + 1] = fmaf(wk, f.y, acc[2 * j + 1]);
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+        for (int j = 0; j < nv; ++j) {
+            const int pj = __shfl_sync(0xffffffffu, pos_c, j);
+            const float wj = __shfl_sync(0xffffffffu, w_c, j);
+            const int4* row = reinterpret_cast<const int4*>(src) + (size_t)pj * n16;
+            int4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = i0 + u * 32 + lane;
+                v[u] = i < n16 ? ld_stream(row + i) : make_int4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t w4[4] = {(uint32_t)v[u].x, (uint32_t)v[u].y, (uint32_t)v[u].z, (uint32_t)v[u].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = bf16x2_to_f2(w4[q]);
+                    acc[u][2 * q] = fmaf(wj, f.x, acc[u][2 * q]);
+                    acc[u][2 * q + 1] = fmaf(wj, f.y, acc[u][2 * q + 1]);
+                }
             }
         }
-        int4 o;
-        o.x = (int)f2_to_bf16x2(acc[0], acc[1]);
-        o.y = (int)f2_to_bf16x2(acc[2], acc[3]);
-        o.z = (int)f2_to_bf16x2(acc[4], acc[5]);
-        o.w = (int)f2_to_bf16x2(acc[6], acc[7]);
-        d[i] = o;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * 32 + lane;
+            if (i >= n16) continue;
+            int4 o;
+            o.x = (int)f2_to_bf16x2(acc[u][0], acc[u][1]);
+            o.y = (int)f2_to_bf16x2(acc[u][2], acc[u][3]);
+            o.z = (int)f2_to_bf16x2(acc[u][4], acc[u][5]);
+            o.w = (int)f2_to_bf16x2(acc[u][6], acc[u][7]);
+            d[i] = o;
+        }
     }
 }
 

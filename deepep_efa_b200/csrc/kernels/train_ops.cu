@@ -102,14 +102,25 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const __nv_bfloat16* __rest
         if (src >= 0) {
             const int4* ar = reinterpret_cast<const int4*>(a + (size_t)src * hidden);
             const int4* br = reinterpret_cast<const int4*>(b + (size_t)(p / num_k) * hidden);
-            for (int i = lane; i < hidden / 8; i += 32) {
-                const int4 x = ar[i], y = br[i];
-                const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
-                const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+            const int n16 = hidden / 8;
+            constexpr int U = 4;  // four column chunks of both rows in flight per lane
+            for (int i0 = 0; i0 < n16; i0 += 32 * U) {
+                int4 x[U], y[U];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 xf = __bfloat1622float2(xp[j]), yf = __bfloat1622float2(yp[j]);
-                    acc = fmaf(xf.x, yf.x, fmaf(xf.y, yf.y, acc));
+                for (int u = 0; u < U; ++u) {
+                    const int i = i0 + u * 32 + lane;
+                    x[u] = i < n16 ? ar[i] : make_int4(0, 0, 0, 0);
+                    y[u] = i < n16 ? br[i] : make_int4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x[u]);
+                    const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y[u]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 xf = __bfloat1622float2(xp[j]), yf = __bfloat1622float2(yp[j]);
+                        acc = fmaf(xf.x, yf.x, fmaf(xf.y, yf.y, acc));
+                    }
                 }
             }
         }

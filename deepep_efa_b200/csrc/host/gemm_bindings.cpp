@@ -120,6 +120,12 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     {
         const char* o = std::getenv("DEEPEP_GEMM_ORDER");
         p.tile_order = (o != nullptr && o[0] == '1') ? 1 : 0;
+        // CTA pairs (cta_group::2) pay off for BF16 with about a thousand rows per expert or more (+1-3 % in a power-limited loop); the FP8 path hands a
+        // window to the epilogue every K block, and the cross-CTA handshake per block costs more than the halved B traffic saves
+        const char* pr = std::getenv("DEEPEP_GEMM_PAIR");
+        if (pr != nullptr && (pr[0] == '0' || pr[0] == '1')) p.cta_pairs = pr[0] == '1';
+        else p.cta_pairs = (!fp8 && p.m_ends == nullptr && (mode == 1 || (int64_t)p.m_total >= 1024 * (int64_t)G)) ? 1 : 0;
+        if (p.num_sms < 2) p.cta_pairs = 0;
     }
     p.error_flag = error_flag(device).data_ptr<int>();
     p.timeout_cycles = (long long)(timeout_ms * (double)clock_khz(device));

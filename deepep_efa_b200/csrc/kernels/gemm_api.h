@@ -38,6 +38,7 @@ struct GroupedGemmArgs {
     int k;                    // mode 0: reduction length; mode 1: K_out (rows of B)
     int num_sms;              // persistent grid size
     int tile_order;           // mode 0: 0 = weight tile shared by consecutive CTAs, 1 = activation tile shared
+    int cta_pairs;            // 1 = two CTAs of a cluster share one 256-row MMA (cta_group::2), each staging half of the B tile
     int* error_flag;          // device int, set non-zero when a bounded pipeline wait ran out
     long long timeout_cycles;
 };

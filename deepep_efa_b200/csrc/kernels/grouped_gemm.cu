@@ -137,14 +137,67 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 }
 // Instruction descriptor: fp32 accumulate, A and B K-major, M = 128, N = n.
 template <bool kFp8>
-__device__ __forceinline__ uint32_t make_idesc(int n) {
+__device__ __forceinline__ uint32_t make_idesc(int n, int m = kBlockM) {
     uint32_t d = 0;
     d |= 1u << 4;                          // D format = F32
     d |= (kFp8 ? 0u : 1u) << 7;            // A format: E4M3 (f8f6f4) or BF16 (f16)
     d |= (kFp8 ? 0u : 1u) << 10;           // B format
     d |= (uint32_t)(n >> 3) << 17;         // N / 8
-    d |= (uint32_t)(kBlockM >> 4) << 24;   // M / 16
+    d |= (uint32_t)(m >> 4) << 24;         // M / 16 (256 for a CTA pair)
     return d;
+}
+
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share one 256-row MMA; each stages its own 128 rows of A and HALF
+// of the B tile, so the bytes every SM pulls from L2 per FLOP drop by a third. No load here is a multicast: each CTA's TMA
+// writes only its own shared memory and signals the leader CTA's mbarrier.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t bar_cluster_addr, void* dst, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+template <bool kFp8>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (kFp8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
 }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -186,11 +239,14 @@ struct TileInfo {
     int c_row_end;  // first output row this tile must not write (end of its group; groups need no 128-row alignment)
 };
 
-template <int kBlockN, bool kFp8, bool kSwiGLU>
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair>
 struct Cfg {
-    static constexpr int kBTileBytes = kBlockN * kKBlockBytes;
+    // B rows staged per CTA: a CTA pair splits the tile's N between its two CTAs
+    static constexpr int kBRows = kPair ? kBlockN / 2 : kBlockN;
+    static constexpr int kBTileBytes = kBRows * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kStages = (kBlockN == 256) ? 4 : (kFp8 ? 5 : 6);
+    static constexpr int kStages = kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
+    static constexpr int kTileRows = kPair ? 2 * kBlockM : kBlockM;  // rows of one scheduled tile (both CTAs of a pair)
     // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
     // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
     static constexpr int kWindows = kFp8 ? 4 : 2;
@@ -205,10 +261,13 @@ struct Cfg {
         (size_t)kStages * kStageBytes + (size_t)kEpiWarps * kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
 };
 
-template <int kBlockN, bool kFp8, bool kSwiGLU>
-__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU>::kThreads), 1)
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair>
+__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
-    using C = Cfg<kBlockN, kFp8, kSwiGLU>;
+    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair>;
+    const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader (issues the MMAs of the pair)
+    const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
@@ -234,7 +293,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int a = 0; a < C::kWindows; ++a) {
             mbar_init(&tmem_full[a], 1);
-            mbar_init(&tmem_empty[a], C::kEpiWarps);
+            mbar_init(&tmem_empty[a], kPair ? 2 * C::kEpiWarps : C::kEpiWarps);  // the leader collects both CTAs' epilogue warps
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         tma_prefetch_desc(&map_a);
@@ -242,21 +301,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // tile table
         int run = 0;
         const int tiles_n = p.mode == 0 ? p.n / kBlockN : 0;
-        const int tiles_fixed = p.mode == 1 ? (p.n / kBlockM) * (p.k / kBlockN) : 0;
+        const int tiles_fixed = p.mode == 1 ? ((p.n + C::kTileRows - 1) / C::kTileRows) * (p.k / kBlockN) : 0;
         for (int g = 0; g < G; ++g) {
             tile_start[g] = run;
             if (p.mode == 0) {
                 const int rows = (p.m_ends != nullptr ? p.m_ends[g] : p.m_offsets[g + 1]) - p.m_offsets[g];
-                run += ((max(rows, 0) + kBlockM - 1) / kBlockM) * tiles_n;
+                run += ((max(rows, 0) + C::kTileRows - 1) / C::kTileRows) * tiles_n;
             } else {
                 run += tiles_fixed;
             }
         }
         tile_start[G] = run;
     }
-    if (warp == 1) tmem_alloc(&s_tmem_base, C::kTmemCols);
+    if (warp == 1) {
+        if constexpr (kPair) tmem_alloc_pair(&s_tmem_base, C::kTmemCols);
+        else tmem_alloc(&s_tmem_base, C::kTmemCols);
+    }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     const int total_tiles = tile_start[G];
@@ -270,12 +333,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int m0 = p.m_offsets[g], m1 = (p.mode == 0 && p.m_ends != nullptr) ? max(p.m_ends[g], m0) : p.m_offsets[g + 1];
         ti.group = g;
         if (p.mode == 0) {
-            const int tiles_m = (m1 - m0 + kBlockM - 1) / kBlockM;
+            const int tiles_m = (m1 - m0 + C::kTileRows - 1) / C::kTileRows;
             const int tiles_n_ = p.n / kBlockN;
             // order 0: consecutive tiles share the weight tile (n outer); order 1: they share the activation tile (m outer)
             const int nt = p.tile_order == 0 ? local / tiles_m : local % tiles_n_;
             const int mt = p.tile_order == 0 ? local % tiles_m : local / tiles_n_;
-            ti.a_row = m0 + mt * kBlockM;
+            ti.a_row = m0 + mt * C::kTileRows + (int)cta_rank * kBlockM;
             ti.a_k0 = 0;
             ti.b_k0 = 0;
             ti.num_kb = p.k / elem_per_kb;
@@ -289,7 +352,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 ti.nblock = (nt * half) / 128;
                 ti.nblock2 = (inter + nt * half) / 128;
             } else {
-                ti.b_row = g * p.n + nt * kBlockN;
+                ti.b_row = g * p.n + nt * kBlockN + (int)cta_rank * (kBlockN / 2);  // a pair splits the tile's N
                 ti.b_row2 = 0;
                 ti.c_col = nt * kBlockN;
                 ti.nblock = (nt * kBlockN) / 128;
@@ -298,16 +361,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         } else {
             const int tiles_j = p.k / kBlockN;
             const int it = local / tiles_j, jt = local % tiles_j;
-            ti.a_row = it * kBlockM;
-            ti.b_row = jt * kBlockN;
+            ti.a_row = it * C::kTileRows + (int)cta_rank * kBlockM;
+            ti.b_row = jt * kBlockN + (int)cta_rank * (kBlockN / 2);
             ti.b_row2 = 0;
             ti.a_k0 = m0;
             ti.b_k0 = m0;
             ti.num_kb = (m1 - m0) / elem_per_kb;
-            ti.c_row = g * p.n + it * kBlockM;
-            ti.c_row_end = p.num_groups * p.n;
+            ti.c_row = g * p.n + ti.a_row;
+            ti.c_row_end = min((g + 1) * p.n, p.num_groups * p.n);
             ti.c_col = jt * kBlockN;
             ti.nblock = ti.nblock2 = 0;
+        }
+    };
+
+    // An epilogue warp hands an accumulator window back to the MMA issuer: in a pair that is the leader CTA's barrier.
+    auto release_window = [&](uint64_t* bar) {
+        if constexpr (kPair) {
+            if (cta_rank == 0) mbar_arrive(bar);
+            else mbar_arrive_cluster(mapa_shared(smem_u32(bar), 0));
+        } else {
+            mbar_arrive(bar);
         }
     };
 
@@ -317,7 +390,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0, phase = 0, g = 0;
             TileInfo ti;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
                 decode(tile, g, ti);
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, limit)) {
@@ -326,6 +399,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     uint8_t* sa = stage_base + (size_t)stage * C::kStageBytes;
                     uint8_t* sb = sa + kATileBytes;
+                    if constexpr (kPair) {
+                        // both CTAs fill their own stage and signal the LEADER's barrier, which expects the bytes of both
+                        const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0);
+                        if (cta_rank == 0) mbar_expect_tx(&full[stage], 2 * C::kStageBytes);
+                        tma_load_2d_pair(&map_a, leader_full, sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
+                        tma_load_2d_pair(&map_b, leader_full, sb, ti.b_k0 + kb * elem_per_kb,
+                                         (kSwiGLU && cta_rank == 1) ? ti.b_row2 : ti.b_row);  // SwiGLU: gate half / up half
+                        if (++stage == C::kStages) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                        continue;
+                    }
                     mbar_expect_tx(&full[stage], C::kStageBytes);
                     tma_load_2d(&map_a, &full[stage], sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
                     if (kSwiGLU) {
@@ -341,7 +427,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
             // Own copies in flight land in this CTA's shared memory: wait for them before the CTA may exit.
-            if (!ok) {
+            if (!ok && kPair && cta_rank == 1) {
+                const long long t0 = clock64();  // the peer's copies signal the leader's barriers: give them a bounded time
+                while (clock64() - t0 < 400000) {
+                }
+            } else if (!ok) {
                 for (int s = 0; s < C::kStages; ++s) {
                     const long long t0 = clock64();
                     while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && clock64() - t0 < limit) {
@@ -351,13 +441,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc<kFp8>(kBlockN);
+        if (lane == 0 && cta_rank == 0) {
+            const uint32_t idesc = make_idesc<kFp8>(kBlockN, C::kTileRows);
             int stage = 0, phase = 0, g = 0;
             int win = 0, win_phase = 0;  // accumulator window ring
             TileInfo ti;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
                 decode(tile, g, ti);
                 if (ti.num_kb == 0) continue;  // epilogue writes zeros on its own
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
@@ -381,13 +471,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // +32 bytes along K inside the swizzle atom = +2 in the 16-byte start-address field
-                        umma<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
-                                   (new_window && j == 0) ? 0u : 1u);
+                        if constexpr (kPair)
+                            umma_pair<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                            (new_window && j == 0) ? 0u : 1u);
+                        else
+                            umma<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                       (new_window && j == 0) ? 0u : 1u);
                     }
-                    umma_commit(&empty[stage]);  // smem stage reusable once these MMAs have read it
+                    // smem stage reusable once these MMAs have read it (in both CTAs of a pair)
+                    if constexpr (kPair) {
+                        umma_commit_pair(smem_u32(&empty[stage]));
+                        umma_commit_pair(mapa_shared(smem_u32(&empty[stage]), 1));
+                    } else {
+                        umma_commit(&empty[stage]);
+                    }
                     const bool window_done = kFp8 ? true : (kb == ti.num_kb - 1);
                     if (window_done) {
-                        umma_commit(&tmem_full[win]);
+                        if constexpr (kPair) {
+                            umma_commit_pair(smem_u32(&tmem_full[win]));
+                            umma_commit_pair(mapa_shared(smem_u32(&tmem_full[win]), 1));
+                        } else {
+                            umma_commit(&tmem_full[win]);
+                        }
                         if (++win == C::kWindows) {
                             win = 0;
                             win_phase ^= 1;
@@ -411,7 +516,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.c);
         const int ldc = p.mode == 0 ? (kSwiGLU ? p.n / 2 : p.n) : p.k;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
             decode(tile, g, ti);
             const int row = ti.c_row + row_in_tile;
             __nv_bfloat16* crow = cbase + (size_t)row * ldc + ti.c_col;
@@ -450,7 +555,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&tmem_empty[win]);  // the window is free as soon as it sits in registers
+                    if (lane == 0) release_window(&tmem_empty[win]);  // the window is free as soon as it sits in registers
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         acc[i] = fmaf(__uint_as_float(v[i]), s_lo, acc[i]);
@@ -533,7 +638,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty[win]);
+                if (lane == 0) release_window(&tmem_empty[win]);
                 if (++win == C::kWindows) {
                     win = 0;
                     win_phase ^= 1;
@@ -544,10 +649,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // neither CTA leaves while the other may still signal it or read its operands
     if (threadIdx.x == 0 && s_abort && p.error_flag != nullptr) atomicExch(p.error_flag, 1);
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, C::kTmemCols);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, C::kTmemCols);
+        else tmem_dealloc(tmem_base, C::kTmemCols);
     }
 }
 
@@ -583,11 +690,11 @@ bool make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64
     return r == CUDA_SUCCESS;
 }
 
-template <int kBlockN, bool kFp8, bool kSwiGLU>
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair>
 cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
-    using C = Cfg<kBlockN, kFp8, kSwiGLU>;
+    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair>;
     CUtensorMap map_a, map_b;
-    const uint32_t b_box_rows = kSwiGLU ? kBlockN / 2 : kBlockN;
+    const uint32_t b_box_rows = (kSwiGLU || kPair) ? kBlockN / 2 : kBlockN;
     bool ok;
     if (a.mode == 0) {
         ok = make_map(&map_a, a.a, kFp8, (uint64_t)a.m_total, (uint64_t)a.k, kBlockM) &&
@@ -597,7 +704,7 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
              make_map(&map_b, a.b, kFp8, (uint64_t)a.k, (uint64_t)a.m_total, b_box_rows);
     }
     if (!ok) return cudaErrorInvalidValue;
-    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU>;
+    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU, kPair>;
     static bool smem_opted_in[64] = {};  // per device, once: the attribute is sticky
     int dev = 0;
     cudaGetDevice(&dev);
@@ -606,8 +713,32 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) smem_opted_in[dev] = true;
     }
-    kernel<<<a.num_sms, C::kThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
-    return cudaGetLastError();
+    if constexpr (kPair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(a.num_sms & ~1), 1, 1);  // whole CTA pairs
+        cfg.blockDim = dim3(C::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cfg.gridDim.x < 2) return cudaErrorInvalidValue;
+        return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, a);
+    } else {
+        kernel<<<a.num_sms, C::kThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
+        return cudaGetLastError();
+    }
+}
+
+// kPair chosen at run time (GroupedGemmArgs::cta_pairs)
+template <int kBlockN, bool kFp8, bool kSwiGLU>
+cudaError_t launch_sel(const GroupedGemmArgs& a, cudaStream_t stream) {
+    if (a.cta_pairs) return launch_impl<kBlockN, kFp8, kSwiGLU, true>(a, stream);
+    return launch_impl<kBlockN, kFp8, kSwiGLU, false>(a, stream);
 }
 
 }  // namespace
@@ -622,24 +753,24 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
             if (a.a_scales == nullptr || a.b_scales == nullptr || a.k % 128 != 0) return cudaErrorInvalidValue;
             if (a.swiglu) {
                 if ((a.n / 2) % 128 != 0) return cudaErrorInvalidValue;  // gate/up halves must start on scale-block boundaries
-                return launch_impl<128, true, true>(a, stream);
+                return launch_sel<128, true, true>(a, stream);
             }
             if (a.n % 128 != 0) return cudaErrorInvalidValue;
-            return launch_impl<128, true, false>(a, stream);
+            return launch_sel<128, true, false>(a, stream);
         }
         if (a.swiglu) {
-            if ((a.n / 2) % 128 == 0) return launch_impl<256, false, true>(a, stream);
-            if ((a.n / 2) % 64 == 0) return launch_impl<128, false, true>(a, stream);
+            if ((a.n / 2) % 128 == 0) return launch_sel<256, false, true>(a, stream);
+            if ((a.n / 2) % 64 == 0) return launch_sel<128, false, true>(a, stream);
             return cudaErrorInvalidValue;
         }
-        if (a.n % 256 == 0) return launch_impl<256, false, false>(a, stream);
-        if (a.n % 128 == 0) return launch_impl<128, false, false>(a, stream);
+        if (a.n % 256 == 0) return launch_sel<256, false, false>(a, stream);
+        if (a.n % 128 == 0) return launch_sel<128, false, false>(a, stream);
         return cudaErrorInvalidValue;
     }
     // K-grouped (weight gradients), bf16 only
     if (a.fp8 || a.swiglu || a.n % kBlockM != 0) return cudaErrorInvalidValue;
-    if (a.k % 256 == 0) return launch_impl<256, false, false>(a, stream);
-    if (a.k % 128 == 0) return launch_impl<128, false, false>(a, stream);
+    if (a.k % 256 == 0) return launch_sel<256, false, false>(a, stream);
+    if (a.k % 128 == 0) return launch_sel<128, false, false>(a, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -31,9 +31,10 @@ def _free_port():
 def test_reference_script_passes_against_this_library(script, extra):
     if not (REF_TESTS / script).is_file():
         pytest.skip("reference test scripts not present (run baseline/build_reference.py)")
-    world = 8 if torch.cuda.device_count() >= 8 else (4 if torch.cuda.device_count() >= 4 else 2)
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
+    # two ranks by default (enough to cross NVLink and quick); DEEPEP_TEST_REF_WORLD=4|8 runs the scripts' full size
+    world = min(int(os.environ.get("DEEPEP_TEST_REF_WORLD", "2")), torch.cuda.device_count())
     env = os.environ.copy()
     env["PYTHONPATH"] = os.pathsep.join([str(ROOT / "deepep_efa_b200" / "compat"), str(ROOT), env.get("PYTHONPATH", "")])
     env.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="1", RANK="0", NCCL_NVLS_ENABLE="0")

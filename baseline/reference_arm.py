@@ -27,7 +27,8 @@ REF_DIR = os.path.join(HERE, "_ref")
 
 def _unavailable(reason: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+        import bench as B
+        B.emit({"impl": "reference", "unavailable": reason})
 
 
 def _import_reference():
@@ -127,7 +128,7 @@ def main(args) -> None:
         except Exception as e:
             result["normal"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
     if rank == 0:
-        print(json.dumps(result), flush=True)
+        B.emit(result)
     try:
         buf.destroy()
     except Exception:

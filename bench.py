@@ -27,8 +27,11 @@ import tempfile
 import threading
 import time
 
-import torch
-import torch.distributed as dist
+# stdout carries exactly one JSON line: whatever NCCL wants to log (its version banner, NCCL_DEBUG output) goes to stderr
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -104,6 +107,14 @@ def physical_gpu_index(local_rank: int) -> int:
         except (ValueError, IndexError):
             return local_rank
     return local_rank
+
+
+def emit(obj) -> None:
+    """Write the result line to the process's original stdout (kept on the sys module: this file can be loaded twice, as
+    __main__ and as 'bench')."""
+    stream = getattr(sys, "_deepep_result_stream", None) or sys.stdout
+    stream.write(json.dumps(obj) + "\n")
+    stream.flush()
 
 
 def ramp_clocks(local_rank: int, max_seconds: float = 12.0) -> None:
@@ -336,7 +347,7 @@ def run_ours(args):
         "impl": "deepep_efa_b200",
     }
     if rank == 0:
-        print(json.dumps(result), flush=True)
+        emit(result)
     buf.destroy()
     dist.destroy_process_group()
 
@@ -418,4 +429,9 @@ def main():
 
 
 if __name__ == "__main__":
+    # Libraries (NCCL's version banner among them) write to file descriptor 1 behind Python's back; the contract is ONE
+    # JSON line on stdout. Keep a private handle on the real stdout for that line and point fd 1 at stderr for everything else.
+    sys._deepep_result_stream = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
     main()

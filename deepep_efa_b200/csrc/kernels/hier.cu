@@ -14,7 +14,7 @@
 // Reference counterparts (csrc/kernels/efa_kernels.cu): moe_routing_sort_kernel + prefix_sum_kernel +
 // scatter_token_ids_kernel (:220-318, three launches, the last one single-threaded per rank, ending in a host
 // sync), topk_remap_kernel (:339-387), build_recv_src_meta_kernel (:448-482), efa_permute_kernel (:405-435).
-// Here the sort is one launch without atomics or host round trip, and every CTA derives its own base offset.
+// Here the sort is one launch without global atomics or host round trip, and every CTA derives its own base offset.
 #include "api.h"
 #include "prims.cuh"
 
@@ -29,65 +29,61 @@ __device__ __forceinline__ bool in_group(const bool* member, int t, int g, int r
     return any;
 }
 
+// Grid = (token chunks of 1024, groups). CTA (b, g) places the members of group g among tokens [1024 b, 1024 b + 1024).
+// Its base offset = all pairs of earlier groups + the group's members among earlier tokens, which it counts itself from
+// the membership matrix (L2-resident re-reads instead of a second launch or inter-CTA waiting).
 __global__ void __launch_bounds__(kSortThreads) routing_sort_kernel(const RoutingSortArgs a) {
     __shared__ int s_warp[32];
-    __shared__ int s_base, s_own;
-    const int g = blockIdx.x, G = a.num_groups, T = a.num_tokens;
+    __shared__ int s_base, s_group_total;
+    const int g = blockIdx.y, G = a.num_groups, T = a.num_tokens;
+    const int t_begin = blockIdx.x * kSortThreads;
     const int ranks_total = G * a.ranks_per_group;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-    // pass 1: how many pairs sort before this group's first entry, and how many entries the group has
-    int before = 0, own = 0;
+    int before = 0, total = 0;
     for (int t = threadIdx.x; t < T; t += kSortThreads) {
         for (int c = 0; c < g; ++c) before += in_group(a.member, t, c, ranks_total, a.ranks_per_group) ? 1 : 0;
-        own += in_group(a.member, t, g, ranks_total, a.ranks_per_group) ? 1 : 0;
+        const int mine = in_group(a.member, t, g, ranks_total, a.ranks_per_group) ? 1 : 0;
+        total += mine;
+        if (t < t_begin) before += mine;
     }
     before = warp_sum(before);
-    own = warp_sum(own);
+    total = warp_sum(total);
     if (threadIdx.x == 0) {
         s_base = 0;
-        s_own = 0;
+        s_group_total = 0;
     }
     __syncthreads();
     if (lane == 0) {
         atomicAdd(&s_base, before);
-        atomicAdd(&s_own, own);
+        atomicAdd(&s_group_total, total);
     }
     __syncthreads();
     const int base = s_base;
-    if (threadIdx.x == 0) {
-        a.counts[g] = s_own;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        a.counts[g] = s_group_total;
         a.prefix[g] = base;
-        if (g == G - 1) a.prefix[G] = base + s_own;
+        if (g == G - 1) a.prefix[G] = base + s_group_total;
     }
 
-    // pass 2: ordered scatter of this group's tokens
-    int running = base;
-    for (int t0 = 0; t0 < T; t0 += kSortThreads) {
-        const int t = t0 + threadIdx.x;
-        const bool flag = t < T && in_group(a.member, t, g, ranks_total, a.ranks_per_group);
-        const unsigned ballot = __ballot_sync(0xffffffffu, flag);
-        __syncthreads();  // s_warp of the previous chunk has been read
-        if (lane == 0) s_warp[warp] = __popc(ballot);
-        __syncthreads();
-        int warp_off = 0, chunk_total = 0;
-        for (int w = 0; w < kSortThreads / 32; ++w) {
-            const int c = s_warp[w];
-            if (w < warp) warp_off += c;
-            chunk_total += c;
-        }
-        if (t < T) {
-            const int slot = running + warp_off + __popc(ballot & ((1u << lane) - 1u));
-            if (flag) a.sorted_ids[slot] = t;
-            if (a.pos != nullptr) a.pos[(size_t)t * G + g] = flag ? slot : -1;
-        }
-        running += chunk_total;
+    const int t = t_begin + threadIdx.x;
+    const bool flag = t < T && in_group(a.member, t, g, ranks_total, a.ranks_per_group);
+    const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+    if (lane == 0) s_warp[warp] = __popc(ballot);
+    __syncthreads();
+    int warp_off = 0;
+    for (int w = 0; w < warp; ++w) warp_off += s_warp[w];
+    if (t < T) {
+        const int slot = base + warp_off + __popc(ballot & ((1u << lane) - 1u));
+        if (flag) a.sorted_ids[slot] = t;
+        if (a.pos != nullptr) a.pos[(size_t)t * G + g] = flag ? slot : -1;
     }
 }
 
 cudaError_t launch_routing_sort(const RoutingSortArgs& a, cudaStream_t stream) {
     if (a.num_groups < 1 || a.ranks_per_group < 1) return cudaErrorInvalidValue;
-    routing_sort_kernel<<<a.num_groups, kSortThreads, 0, stream>>>(a);
+    const int chunks = a.num_tokens > 0 ? (a.num_tokens + kSortThreads - 1) / kSortThreads : 1;
+    routing_sort_kernel<<<dim3(chunks, a.num_groups), kSortThreads, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

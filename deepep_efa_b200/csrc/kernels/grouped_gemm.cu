@@ -540,7 +540,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float* sa_row = p.a_scales + (size_t)min(row, p.m_total - 1) * num_kscales;
                 const float* sb0 = p.b_scales + ((size_t)ti.group * n_blocks + ti.nblock) * num_kscales;
                 const float* sb1 = p.b_scales + ((size_t)ti.group * n_blocks + ti.nblock2) * num_kscales;
+                // A warp whose 32 rows all lie past the end of the group (masked low-latency layout: a handful of valid rows
+                // per expert) only keeps the window ring moving; it promotes nothing.
+                const bool warp_has_rows = ti.c_row + q * 32 < ti.c_row_end;
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
+                    if (!warp_has_rows) {
+                        if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
+                            ok = false;
+                            break;
+                        }
+                        __syncwarp();
+                        if (lane == 0) release_window(&tmem_empty[win]);
+                        if (++win == C::kWindows) {
+                            win = 0;
+                            win_phase ^= 1;
+                        }
+                        continue;
+                    }
                     const float sa = __ldg(sa_row + kb);
                     const float s_lo = sa * __ldg(sb0 + kb), s_hi = kSwiGLU ? sa * __ldg(sb1 + kb) : s_lo;
                     if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {

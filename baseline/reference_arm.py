@@ -85,7 +85,7 @@ def main(args) -> None:
 
     try:
         B.ramp_clocks(local_rank)
-        sampler = B.ClockSampler() if rank == 0 else None
+        sampler = B.ClockSampler(gpus={B.physical_gpu_index(r) for r in range(world)}) if rank == 0 else None
         if sampler is not None:
             sampler.start()
         for _ in range(warmup):

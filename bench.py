@@ -45,28 +45,81 @@ PUBLISHED_LL_US = 1145.0  # reference README.md:83, EP16 on 2 nodes (no single-n
 # clocks
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with one nvidia-smi process (all GPUs, time-stamped lines) while a region
-    runs; ``stop(gpus)`` keeps the lines of the given physical GPU indices."""
+    """Samples SM clocks and throttle reasons of the given physical GPUs while a region runs; settings are only READ.
+
+    A thread polls NVML every ``period_ms`` (the first sample is taken inside ``start``, so even a region of a few
+    milliseconds has one); if NVML cannot be loaded, one ``nvidia-smi -lms`` process for all GPUs is used instead, which
+    needs a second or two before its first line."""
 
     FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits (nvml.h: nvmlClocksEventReason*)
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, period_ms: int = 100):
+    def __init__(self, period_ms: int = 20, gpus=None):
         self.period_ms = period_ms
+        self.gpus = sorted(gpus) if gpus is not None else None
         self.proc, self.path = None, None
+        self._nvml, self._handles, self._thread = None, [], None
+        self._stop = threading.Event()
+        self._sm, self._smax, self._reasons = [], [], set()
+
+    def _sample_nvml(self):
+        n = self._nvml
+        for h in self._handles:
+            try:
+                self._sm.append(float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)))
+                self._smax.append(float(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)))
+                get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+                bits = int(get(h))
+                for name, bit in self.REASON_BITS.items():
+                    if bits & bit:
+                        self._reasons.add(name)
+            except Exception:
+                pass
+
+    def _loop(self):
+        while not self._stop.wait(self.period_ms / 1e3):
+            self._sample_nvml()
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            count = pynvml.nvmlDeviceGetCount()
+            ids = self.gpus if self.gpus is not None else list(range(count))
+            self._handles = [pynvml.nvmlDeviceGetHandleByIndex(i) for i in ids if i < count]
+            self._nvml = pynvml
+            self._sample_nvml()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._nvml = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms",
-                                          str(self.period_ms)], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          str(max(self.period_ms, 100))], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self, gpus):
+    def stop(self, gpus=None):
         res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self._nvml is not None:
+            self._stop.set()
+            if self._thread is not None:
+                self._thread.join(timeout=2)
+            self._sample_nvml()
+            try:
+                self._nvml.nvmlShutdown()
+            except Exception:
+                pass
+            if self._sm:
+                res.update(sm_mhz=statistics.median(self._sm), sm_max_mhz=max(self._smax), reasons=sorted(self._reasons),
+                           samples=len(self._sm))
+            return res
         if self.proc is None:
             return res
         self.proc.terminate()
@@ -82,7 +135,7 @@ class ClockSampler:
                 if len(p) < 9:
                     continue
                 try:
-                    if int(p[1]) not in gpus:
+                    if gpus is not None and int(p[1]) not in gpus:
                         continue
                     sm.append(float(p[2])), smax.append(float(p[3]))
                 except ValueError:
@@ -243,7 +296,7 @@ def run_ours(args):
     # one sampler (rank 0) for all GPUs of the job; it runs from the warm-up through both timed regions (device-timed and
     # end-to-end), which execute the same workload back to back
     ramp_clocks(local_rank)
-    sampler = ClockSampler() if rank == 0 else None
+    sampler = ClockSampler(gpus={physical_gpu_index(r) for r in range(world)}) if rank == 0 else None
     if sampler is not None:
         sampler.start()
     for _ in range(warmup):

@@ -121,3 +121,29 @@ def test_transport_stubs_and_domain_limits():
     with pytest.raises(AssertionError, match="at most 8"):
         ep.Buffer(fake_group, num_nvl_ranks=16)
     assert ep.Buffer.get_dispatch_config(16) is not None and ep.Buffer.get_combine_config(64) is not None
+
+
+def test_clock_sampler_reads_a_fake_nvml(monkeypatch):
+    """The benchmark's clock record comes from NVML reads only; a fake NVML shows median, maximum and reasons."""
+    import sys
+    import time
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.calls = []
+    fake.nvmlInit = lambda: fake.calls.append("init")
+    fake.nvmlShutdown = lambda: fake.calls.append("shutdown")
+    fake.nvmlDeviceGetCount = lambda: 8
+    fake.nvmlDeviceGetHandleByIndex = lambda i: i
+    fake.nvmlDeviceGetClockInfo = lambda h, k: 1900 + h
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, k: 1965
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0x4 if h == 3 else 0
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    s = bench.ClockSampler(period_ms=5, gpus={0, 3})
+    s.start()
+    time.sleep(0.05)
+    rec = s.stop()
+    assert rec["samples"] >= 4 and rec["sm_max_mhz"] == 1965 and 1900 <= rec["sm_mhz"] <= 1903
+    assert rec["reasons"] == ["sw_power_cap"]
+    assert fake.calls == ["init", "shutdown"]  # nothing but reads in between

@@ -30,6 +30,8 @@ def main():
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--native-scaling", action="store_true",
+                    help="fp8 only: power-of-two scales applied by the tensor core (UE8M0 block scaling) instead of per-K-block promotion")
     args = ap.parse_args()
     from deepep_efa_b200 import _ext
     from deepep_efa_b200.ops.grouped_gemm import grouped_gemm
@@ -41,11 +43,20 @@ def main():
     x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(G, N, K, device="cuda") * 0.02).to(torch.bfloat16)
     if args.dtype == "fp8":
-        a, a_s = C.per_token_cast_to_fp8(x, False, False)
+        from deepep_efa_b200.ops.grouped_gemm import build_sf_atoms_a, build_sf_atoms_b
+        a, a_s = C.per_token_cast_to_fp8(x, args.native_scaling, False)
         wb = w.float().view(G, N // 128, 128, K // 128, 128)
         b_s = (wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0).contiguous()
+        if args.native_scaling:
+            b_s = torch.exp2(torch.ceil(torch.log2(b_s))).contiguous()
         b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous()
-        fn = lambda: grouped_gemm(a, b, offs, swiglu=args.swiglu, a_scales=a_s, b_scales=b_s)
+        del wb
+        if args.native_scaling:
+            atoms_b = build_sf_atoms_b(b_s, N, args.swiglu)  # once per weight
+            # the activation atoms are rebuilt on every call, as a layer does
+            fn = lambda: grouped_gemm(a, b, offs, swiglu=args.swiglu, sfa_atoms=build_sf_atoms_a(a_s), sfb_atoms=atoms_b)
+        else:
+            fn = lambda: grouped_gemm(a, b, offs, swiglu=args.swiglu, a_scales=a_s, b_scales=b_s)
     else:
         fn = lambda: grouped_gemm(x, w, offs, swiglu=args.swiglu)
 
@@ -77,7 +88,7 @@ def main():
     except Exception:
         pass
     peak = peaks.get("bf16_tflops", 1590.0)
-    out = {"kernel": "grouped_gemm", "dtype": args.dtype, "swiglu": args.swiglu, "experts": G, "rows_per_expert": R, "k": K, "n": N,
+    out = {"kernel": "grouped_gemm", "dtype": args.dtype, "native_scaling": bool(args.native_scaling), "swiglu": args.swiglu, "experts": G, "rows_per_expert": R, "k": K, "n": N,
            "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_cublas_peak": round(flops / ms / 1e9 / peak, 3)}
     if not args.no_cublas and args.dtype == "bf16" and not args.swiglu:
         def loop():

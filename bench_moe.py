@@ -70,7 +70,7 @@ def run(args):
         nvl = int(1.3 * ((rows_worst * (H + H // 128 * 4 + K * 12 + 4)) + 2 * rows_worst * H * 2)) + (64 << 20)
         buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=nvl, explicitly_destroy=True)
         layer = MoELayer(MoEConfig(hidden=H, intermediate=I, num_experts=E, num_topk=K, init_std=0.02), buf, seed=1)
-        layer.prepare_fp8()
+        layer.prepare_fp8(native_block_scaling=args.native_scaling)
         g = torch.Generator().manual_seed(rank)
         x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
         idx = torch.rand(T, E, generator=g).topk(K, dim=-1).indices.cuda()
@@ -80,7 +80,7 @@ def run(args):
         flops = 2.0 * T * K * H * (2 * I) + 2.0 * T * K * I * H  # per rank on average (uniform routing)
         results.append({
             "metric": "moe_layer_forward_fp8_tokens_per_s", "value": round(T * world / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "dtype": "fp8_e4m3 (bf16 combine)",
+            "steps": args.steps, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "dtype": "fp8_e4m3 (bf16 combine)", "native_scaling": bool(args.native_scaling),
             "expert_gemm_tflops_per_gpu": round(flops / (ms / 1e3) / 1e12, 1),
             "frac_of_measured_bf16_peak": round(flops / (ms / 1e3) / 1e12 / peaks.get("bf16_tflops_sustained", 1408.3), 3),
             "config": {"model": "DeepSeek-V3-shaped MoE layer forward", "tokens_per_rank": T, "hidden": H, "intermediate": I, "num_experts": E,
@@ -121,7 +121,7 @@ def run(args):
         buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=2 << 20, num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(T, H, world, E),
                         low_latency_mode=True, explicitly_destroy=True)
         layer = MoELayer(MoEConfig(hidden=H, intermediate=I, num_experts=E, num_topk=K, init_std=0.02), buf, seed=3)
-        layer.prepare_fp8()
+        layer.prepare_fp8(native_block_scaling=args.native_scaling)
         g = torch.Generator().manual_seed(200 + rank)
         x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
         idx = torch.rand(T, E, generator=g).topk(K, dim=-1).indices.cuda()
@@ -132,7 +132,7 @@ def run(args):
         weight_bytes = L * (2 * I * H + H * I)  # e4m3 expert weights streamed once per step
         results.append({
             "metric": "moe_decode_layer_us", "value": round(ms * 1e3, 1), "unit": "us", "n_gpus": world, "steps": max(args.steps, 20),
-            "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "dtype": "fp8_e4m3 (bf16 combine)",
+            "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "dtype": "fp8_e4m3 (bf16 combine)", "native_scaling": bool(args.native_scaling),
             "weight_stream_GBps_per_gpu": round(weight_bytes / 1e9 / (ms / 1e3), 1),
             "frac_of_measured_hbm": round(weight_bytes / 1e9 / (ms / 1e3) / peaks.get("hbm_gbs", 6551.4), 3),
             "config": {"model": "DeepSeek-V3-shaped MoE layer, decode step through the low-latency path", "tokens_per_rank": T, "hidden": H,
@@ -153,4 +153,6 @@ if __name__ == "__main__":
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default="both", choices=["fwd_fp8", "train_bf16", "decode_ll", "both"])
+    ap.add_argument("--native-scaling", action="store_true",
+                    help="FP8 configs: power-of-two scales applied by the tensor core (UE8M0 block scaling) instead of fp32 scales")
     run(ap.parse_args())

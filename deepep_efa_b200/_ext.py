@@ -35,6 +35,7 @@ CUDA_SOURCES = [
     "kernels/noalloc.cu",
     "kernels/hier.cu",
     "kernels/train_ops.cu",
+    "kernels/sf_atoms.cu",
 ]
 CPP_SOURCES = [
     "host/bindings.cpp",

@@ -59,7 +59,8 @@ int clock_khz(int device) {
 // mode 1: a [N_out, M], b [K_out, M], m_offsets [G+1] -> c [G, N_out, K_out]
 torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& m_offsets, int mode, bool swiglu,
                            c10::optional<torch::Tensor> a_scales, c10::optional<torch::Tensor> b_scales,
-                           c10::optional<torch::Tensor> out, int num_sms, double timeout_ms, c10::optional<torch::Tensor> m_ends) {
+                           c10::optional<torch::Tensor> out, int num_sms, double timeout_ms, c10::optional<torch::Tensor> m_ends,
+                           c10::optional<torch::Tensor> sfa_atoms, c10::optional<torch::Tensor> sfb_atoms) {
     DXG_CHECK(a.is_cuda() && b.is_cuda() && m_offsets.is_cuda(), "operands must be CUDA tensors");
     DXG_CHECK(a.is_contiguous() && b.is_contiguous() && m_offsets.is_contiguous(), "operands must be contiguous");
     DXG_CHECK(m_offsets.scalar_type() == torch::kInt32 && m_offsets.dim() == 1 && m_offsets.numel() >= 2, "m_offsets must be int32 [G+1]");
@@ -90,7 +91,18 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         p.m_total = (int)M;
         p.n = (int)N;
         p.k = (int)K;
-        if (fp8) {
+        if (fp8 && sfa_atoms.has_value()) {
+            // native block scaling: pre-built UE8M0 atoms (build_sf_atoms_a / build_sf_atoms_b)
+            DXG_CHECK(sfb_atoms.has_value(), "sfa_atoms and sfb_atoms go together");
+            DXG_CHECK(K % 128 == 0 && N % 128 == 0, "native block scaling needs K % 128 == 0 and N % 128 == 0");
+            const int64_t tiles_n = swiglu ? (N / 2) / 64 : N / 128;
+            DXG_CHECK(sfa_atoms->is_cuda() && sfa_atoms->scalar_type() == torch::kUInt8 && sfa_atoms->is_contiguous() &&
+                          sfa_atoms->numel() == ((M + 127) / 128) * (K / 128) * 512, "sfa_atoms must be uint8 [ceil(M/128), K/128, 512]");
+            DXG_CHECK(sfb_atoms->is_cuda() && sfb_atoms->scalar_type() == torch::kUInt8 && sfb_atoms->is_contiguous() &&
+                          sfb_atoms->numel() == (int64_t)G * tiles_n * (K / 128) * 512, "sfb_atoms must be uint8 [G, n tiles, K/128, 512]");
+            p.sfa_atoms = sfa_atoms->data_ptr<uint8_t>();
+            p.sfb_atoms = sfb_atoms->data_ptr<uint8_t>();
+        } else if (fp8) {
             DXG_CHECK(a_scales.has_value() && b_scales.has_value(), "fp8 operands need a_scales and b_scales");
             DXG_CHECK(a_scales->scalar_type() == torch::kFloat32 && a_scales->is_contiguous() && a_scales->numel() == M * (K / 128), "a_scales must be f32 [M, K/128]");
             DXG_CHECK(b_scales->scalar_type() == torch::kFloat32 && b_scales->is_contiguous() && b_scales->numel() == (int64_t)G * (N / 128) * (K / 128), "b_scales must be f32 [G, N/128, K/128]");
@@ -247,14 +259,40 @@ torch::Tensor rowdot(const torch::Tensor& a, const torch::Tensor& b, const torch
     return out;
 }
 
+torch::Tensor build_sf_atoms_a(const torch::Tensor& scales) {
+    DXG_CHECK(scales.is_cuda() && scales.scalar_type() == torch::kFloat32 && scales.is_contiguous() && scales.dim() == 2, "scales must be contiguous CUDA f32 [M, K/128]");
+    c10::cuda::CUDAGuard guard(scales.device());
+    const int64_t M = scales.size(0), nkb = scales.size(1);
+    auto atoms = torch::empty({(M + 127) / 128, nkb, 512}, scales.options().dtype(torch::kUInt8));
+    const cudaError_t e = dx::launch_build_sfa_atoms(scales.data_ptr<float>(), atoms.data_ptr<uint8_t>(), (int)M, (int)nkb,
+                                                     at::cuda::getCurrentCUDAStream(scales.get_device()).stream());
+    DXG_CHECK(e == cudaSuccess, "build_sf_atoms_a launch failed");
+    return atoms;
+}
+
+torch::Tensor build_sf_atoms_b(const torch::Tensor& scales, int64_t n, bool swiglu) {
+    DXG_CHECK(scales.is_cuda() && scales.scalar_type() == torch::kFloat32 && scales.is_contiguous() && scales.dim() == 3 && scales.size(1) * 128 == n,
+              "scales must be contiguous CUDA f32 [G, N/128, K/128]");
+    c10::cuda::CUDAGuard guard(scales.device());
+    const int64_t G = scales.size(0), nkb = scales.size(2);
+    const int64_t tiles = swiglu ? (n / 2) / 64 : n / 128;
+    auto atoms = torch::empty({G, tiles, nkb, 512}, scales.options().dtype(torch::kUInt8));
+    const cudaError_t e = dx::launch_build_sfb_atoms(scales.data_ptr<float>(), atoms.data_ptr<uint8_t>(), (int)G, (int)n, (int)nkb, swiglu ? 1 : 0,
+                                                     at::cuda::getCurrentCUDAStream(scales.get_device()).stream());
+    DXG_CHECK(e == cudaSuccess, "build_sf_atoms_b: N (and N/2 with swiglu) must be a multiple of 128");
+    return atoms;
+}
+
 void bind_gemm(py::module_& m) {
+    m.def("build_sf_atoms_a", &build_sf_atoms_a);
+    m.def("build_sf_atoms_b", &build_sf_atoms_b);
     m.def("transpose_bf16", &transpose_bf16);
     m.def("swiglu_fwd", &swiglu_fwd);
     m.def("swiglu_bwd", &swiglu_bwd);
     m.def("rowdot", &rowdot);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
-          py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none());
+          py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none(), py::arg("sfa_atoms") = py::none(), py::arg("sfb_atoms") = py::none());
     m.def("build_plan", &build_plan);
     m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
     m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());

@@ -26,6 +26,11 @@ struct GroupedGemmArgs {
     void* c;                  // bf16 output
     const float* a_scales;    // fp8 only: [M_total, K/128]
     const float* b_scales;    // fp8 only: [G, N/128, K/128]
+    // fp8 with native block scaling (power-of-two scales; mode 0, group starts on multiples of 128 rows): UE8M0 scale atoms,
+    // 512 bytes per (128 rows, 128 K): [ceil(M/128)][K/128][512] and [G][N/128 tiles (swiglu: N/2/64 tiles)][K/128][512];
+    // when sfa_atoms is set the fp32 scale pointers are ignored
+    const uint8_t* sfa_atoms;
+    const uint8_t* sfb_atoms;
     const int* m_offsets;     // [G+1] device memory
     const int* m_ends;        // optional [G]: group g covers rows [m_offsets[g], m_ends[g]) instead of up to m_offsets[g+1]
                               // (mode 0 only; the low-latency layout has fixed group starts and a count per expert)
@@ -68,5 +73,9 @@ cudaError_t launch_swiglu_fwd(const void* h13, void* h, long long rows, int inte
 cudaError_t launch_swiglu_bwd(const void* h13, const void* dh, void* dh13, long long rows, int inter, cudaStream_t stream);
 //   out[n, k] = <a[pos[n, k]], b[n]>  (f32 out, 0 where pos < 0)
 cudaError_t launch_rowdot(const void* a, const void* b, const int* pos, float* out, int n_rows, int num_k, int hidden, cudaStream_t stream);
+
+// Scale atoms of the natively block-scaled FP8 GEMM (sf_atoms.cu); scales must be powers of two.
+cudaError_t launch_build_sfa_atoms(const float* scales, uint8_t* atoms, int rows, int num_kb, cudaStream_t stream);
+cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, cudaStream_t stream);
 
 }  // namespace dx

@@ -200,6 +200,44 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint6
     }
 }
 
+// ---- native block scaling (kind::mxf8f6f4.block_scale): UE8M0 scale factors live in TMEM, one byte per 32 K-elements and
+// row. A 128-row x 128-K scale tile is a 512-byte atom in shared memory: the byte of row (m0 + 32*m1), K sub-block kb sits at
+// m0*16 + m1*4 + kb; tcgen05.cp moves it to four TMEM columns (lane m0, column m1, byte kb), replicated to all four lane
+// quarters. With one scale per 128 K-elements the four bytes of a word are equal.
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src),
+                 "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 rows of 16 bytes, contiguous: no swizzle, 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;            // leading byte offset (one 16-byte column only)
+    d |= (uint64_t)(128 >> 4) << 32;   // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;            // descriptor version
+    return d;                          // layout type 0: no swizzle
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+// Instruction descriptor of the block-scaled kind: E4M3 operands (format 0), K-major, UE8M0 scales, scale-factor ids 0.
+__device__ __forceinline__ uint32_t make_idesc_mx(int n) {
+    uint32_t d = 0;
+    d |= (uint32_t)(n >> 3) << 17;         // N / 8
+    d |= 1u << 23;                         // scale format: E8M0
+    d |= (uint32_t)(kBlockM >> 4) << 24;   // M / 16
+    return d;
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 __device__ __forceinline__ int4 pack8_bf16(const float* o) {
@@ -237,34 +275,39 @@ __device__ __forceinline__ void store_block_coalesced(int4* stage, const int4 (&
 struct TileInfo {
     int a_row, a_k0, b_row, b_row2, b_k0, num_kb, c_row, c_col, group, nblock, nblock2;
     int c_row_end;  // first output row this tile must not write (end of its group; groups need no 128-row alignment)
+    int nt;         // n-tile index inside the group (kMx: selects the B scale atoms)
 };
 
-template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair>
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
 struct Cfg {
+    static constexpr bool kPromote = kFp8 && !kMx;  // FP8 with fp32 scales: every K block is promoted on the CUDA cores
+    static constexpr int kSfBytes = kMx ? 1024 : 0; // per stage: one 512-byte scale atom for A and one for B
     // B rows staged per CTA: a CTA pair splits the tile's N between its two CTAs
     static constexpr int kBRows = kPair ? kBlockN / 2 : kBlockN;
     static constexpr int kBTileBytes = kBRows * kKBlockBytes;
-    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kStages = kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes + kSfBytes;
+    static constexpr int kStages = kMx ? 6 : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
     static constexpr int kTileRows = kPair ? 2 * kBlockM : kBlockM;  // rows of one scheduled tile (both CTAs of a pair)
     // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
     // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
-    static constexpr int kWindows = kFp8 ? 4 : 2;
-    static constexpr int kTmemCols = kWindows * kBlockN;
+    static constexpr int kWindows = kPromote ? 4 : 2;
+    static constexpr int kSfCol0 = kWindows * kBlockN;   // kMx: two alternating sets of (4 columns A + 4 columns B) after the windows
+    static constexpr int kTmemCols = kMx ? 512 : kWindows * kBlockN;
     static constexpr int kOutCols = kSwiGLU ? kBlockN / 2 : kBlockN;
     // FP8 promotes every K block on the CUDA cores, so it gets two epilogue warps per TMEM lane quarter (each takes half
     // of the columns); BF16 reads the accumulator once per tile and one warp per quarter is plenty.
-    static constexpr int kEpiWarps = kFp8 ? 8 : 4;
+    static constexpr int kEpiWarps = kPromote ? 8 : 4;
     static constexpr int kThreads = 64 + 32 * kEpiWarps;
     static constexpr int kOutStageBytes = 4096;    // per epilogue warp: 32 rows x 64 BF16
     static constexpr size_t kSmemBytes =
         (size_t)kStages * kStageBytes + (size_t)kEpiWarps * kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
 };
 
-template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair>
-__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair>::kThreads), 1)
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
+__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
-    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair>;
+    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
+    static_assert(!kMx || (kFp8 && !kPair && kBlockN == 128), "native block scaling: e4m3 operands, single CTA, 128-column tiles");
     const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader (issues the MMAs of the pair)
     const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -339,6 +382,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int nt = p.tile_order == 0 ? local / tiles_m : local % tiles_n_;
             const int mt = p.tile_order == 0 ? local % tiles_m : local / tiles_n_;
             ti.a_row = m0 + mt * C::kTileRows + (int)cta_rank * kBlockM;
+            ti.nt = nt;
             ti.a_k0 = 0;
             ti.b_k0 = 0;
             ti.num_kb = p.k / elem_per_kb;
@@ -413,6 +457,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         continue;
                     }
                     mbar_expect_tx(&full[stage], C::kStageBytes);
+                    if constexpr (kMx) {
+                        // scale atoms: [row tile][K block][512] for A, [group][n tile][K block][512] for B
+                        uint8_t* ssf = sb + C::kBTileBytes;
+                        const size_t nkb = (size_t)(p.k / 128);
+                        bulk_load_1d(ssf, p.sfa_atoms + ((size_t)(ti.a_row >> 7) * nkb + kb) * 512, 512, &full[stage]);
+                        bulk_load_1d(ssf + 512, p.sfb_atoms + (((size_t)ti.group * (p.n / kBlockN) + ti.nt) * nkb + kb) * 512, 512,
+                                     &full[stage]);
+                    }
                     tma_load_2d(&map_a, &full[stage], sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
                     if (kSwiGLU) {
                         tma_load_2d(&map_b, &full[stage], sb, ti.b_k0 + kb * elem_per_kb, ti.b_row);
@@ -442,7 +494,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0 && cta_rank == 0) {
-            const uint32_t idesc = make_idesc<kFp8>(kBlockN, C::kTileRows);
+            const uint32_t idesc = kMx ? make_idesc_mx(kBlockN) : make_idesc<kFp8>(kBlockN, C::kTileRows);
+            int sf_buf = 0;
             int stage = 0, phase = 0, g = 0;
             int win = 0, win_phase = 0;  // accumulator window ring
             TileInfo ti;
@@ -451,7 +504,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 decode(tile, g, ti);
                 if (ti.num_kb == 0) continue;  // epilogue writes zeros on its own
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
-                    const bool new_window = kFp8 ? true : (kb == 0);
+                    const bool new_window = C::kPromote ? true : (kb == 0);
                     if (new_window) {
                         if (!mbar_wait(&tmem_empty[win], win_phase ^ 1, abort_flag, limit)) {
                             ok = false;
@@ -468,15 +521,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t sb = sa + kATileBytes;
                     const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
                     const uint32_t tmem_d = tmem_base + (uint32_t)(win * kBlockN);
+                    if constexpr (kMx) {
+                        // scale atoms of this stage -> TMEM (alternating column sets), then four K=32 MMAs that read them
+                        const uint32_t ssf = sb + C::kBTileBytes;
+                        const uint32_t t_sfa = tmem_base + (uint32_t)(C::kSfCol0 + sf_buf * 8), t_sfb = t_sfa + 4;
+                        tmem_cp_sf(t_sfa, make_sf_desc(ssf));
+                        tmem_cp_sf(t_sfb, make_sf_desc(ssf + 512));
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // +32 bytes along K inside the swizzle atom = +2 in the 16-byte start-address field
-                        if constexpr (kPair)
-                            umma_pair<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
-                                            (new_window && j == 0) ? 0u : 1u);
-                        else
-                            umma<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
-                                       (new_window && j == 0) ? 0u : 1u);
+                        for (int j = 0; j < 4; ++j)
+                            umma_mx(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, t_sfa, t_sfb,
+                                    (new_window && j == 0) ? 0u : 1u);
+                        sf_buf ^= 1;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // +32 bytes along K inside the swizzle atom = +2 in the 16-byte start-address field
+                            if constexpr (kPair)
+                                umma_pair<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                                (new_window && j == 0) ? 0u : 1u);
+                            else
+                                umma<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                           (new_window && j == 0) ? 0u : 1u);
+                        }
                     }
                     // smem stage reusable once these MMAs have read it (in both CTAs of a pair)
                     if constexpr (kPair) {
@@ -485,7 +551,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     } else {
                         umma_commit(&empty[stage]);
                     }
-                    const bool window_done = kFp8 ? true : (kb == ti.num_kb - 1);
+                    const bool window_done = C::kPromote ? true : (kb == ti.num_kb - 1);
                     if (window_done) {
                         if constexpr (kPair) {
                             umma_commit_pair(smem_u32(&tmem_full[win]));
@@ -525,7 +591,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int c = 0; c < C::kOutCols; c += 8) *reinterpret_cast<int4*>(crow + c) = make_int4(0, 0, 0, 0);
                 continue;
             }
-            if constexpr (kFp8) {
+            if constexpr (C::kPromote) {
                 // One window per K block, promoted into fp32 registers with the two scales. A warp owns two 32-column
                 // chunks: with SwiGLU a gate chunk and the matching up chunk, otherwise two neighbouring chunks.
                 constexpr int kLo0 = 0, kHalfCols = kBlockN / 2;
@@ -706,9 +772,9 @@ bool make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64
     return r == CUDA_SUCCESS;
 }
 
-template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair>
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
 cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
-    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair>;
+    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
     CUtensorMap map_a, map_b;
     const uint32_t b_box_rows = (kSwiGLU || kPair) ? kBlockN / 2 : kBlockN;
     bool ok;
@@ -720,7 +786,7 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
              make_map(&map_b, a.b, kFp8, (uint64_t)a.k, (uint64_t)a.m_total, b_box_rows);
     }
     if (!ok) return cudaErrorInvalidValue;
-    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU, kPair>;
+    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
     static bool smem_opted_in[64] = {};  // per device, once: the attribute is sticky
     int dev = 0;
     cudaGetDevice(&dev);
@@ -765,6 +831,12 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
     const int kb = a.fp8 ? 128 : 64;
     if (a.mode == 0) {
         if (a.k % kb != 0) return cudaErrorInvalidValue;
+        if (a.fp8 && a.sfa_atoms != nullptr) {
+            // native block scaling: pre-built UE8M0 scale atoms, every group starts on a multiple of 128 rows
+            if (a.sfb_atoms == nullptr || a.k % 128 != 0 || a.n % 128 != 0) return cudaErrorInvalidValue;
+            if (a.swiglu) return launch_impl<128, true, true, false, true>(a, stream);
+            return launch_impl<128, true, false, false, true>(a, stream);
+        }
         if (a.fp8) {
             if (a.a_scales == nullptr || a.b_scales == nullptr || a.k % 128 != 0) return cudaErrorInvalidValue;
             if (a.swiglu) {

@@ -156,8 +156,14 @@ class MoELayer(nn.Module):
         return None
 
     # -- FP8 inference path -------------------------------------------------------------------------------------
-    def prepare_fp8(self) -> None:
-        """Quantise the expert weights to e4m3 with one fp32 scale per 128x128 block (done once)."""
+    def prepare_fp8(self, native_block_scaling: bool = False) -> None:
+        """Quantise the expert weights to e4m3 with one fp32 scale per 128x128 block (done once).
+
+        ``native_block_scaling=True`` rounds every scale up to a power of two and builds the UE8M0 scale atoms the tensor
+        core reads directly (``tcgen05.mma kind::mxf8f6f4.block_scale``); ``forward_fp8`` then quantises activations with
+        power-of-two scales as well and the GEMMs accumulate a whole tile in TMEM instead of promoting every K block."""
+        self._mx = None
+
         def q(w):
             G, N, K = w.shape
             out = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device=w.device)
@@ -165,10 +171,15 @@ class MoELayer(nn.Module):
             for e in range(G):  # per expert: bounded fp32 temporaries
                 wb = w[e].detach().float().view(N // 128, 128, K // 128, 128)
                 s = (wb.abs().amax(dim=(1, 3)).clamp(min=1e-4) / 448.0)
+                if native_block_scaling:
+                    s = torch.exp2(torch.ceil(torch.log2(s)))
                 out[e] = (wb / s.view(N // 128, 1, K // 128, 1)).view(N, K).to(torch.float8_e4m3fn)
                 scales[e] = s
             return out, scales
         self._fp8 = (q(self.w13), q(self.w2))
+        if native_block_scaling:
+            (_, s13), (_, s2) = self._fp8
+            self._mx = (gg.build_sf_atoms_b(s13, self.w13.size(1), swiglu=True), gg.build_sf_atoms_b(s2, self.w2.size(1)))
 
     @torch.no_grad()
     def forward_fp8(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -181,16 +192,23 @@ class MoELayer(nn.Module):
         if topk_idx is None:
             topk_idx, topk_weights = self.route(x)
         buf = self.buffer
+        mx = getattr(self, "_mx", None)
         per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(topk_idx, self.cfg.num_experts)
         (rx, rs), recv_idx, recv_w, counts, handle, _ = buf.dispatch(
             x, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert, topk_idx=topk_idx,
-            topk_weights=topk_weights, expert_alignment=EXPERT_ALIGNMENT, quantize_fp8=True)
+            topk_weights=topk_weights, expert_alignment=EXPERT_ALIGNMENT, quantize_fp8=True, round_scale=mx is not None)
         plan = build_expert_plan(recv_idx, counts)
         a = gather_rows(rx, plan.src_row)
         a_s = gather_rows(rs, plan.src_row) if rs.size(1) % 4 == 0 else rs.index_select(0, plan.src_row.clamp(min=0).long())
-        h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, a_scales=a_s, b_scales=s13)
-        hq, hs = C.per_token_cast_to_fp8(h, False, False)
-        y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, a_scales=hs, b_scales=s2)
+        if mx is not None:
+            # padding rows of the plan carry all-zero data; whatever exponent their zero scale maps to does not matter
+            h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[0])
+            hq, hs = C.per_token_cast_to_fp8(h, True, False)
+            y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, sfa_atoms=gg.build_sf_atoms_a(hs), sfb_atoms=mx[1])
+        else:
+            h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, a_scales=a_s, b_scales=s13)
+            hq, hs = C.per_token_cast_to_fp8(h, False, False)
+            y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, a_scales=hs, b_scales=s2)
         y_recv = unpermute_weighted(y_perm, recv_w, plan, buf.empty_symmetric([rx.size(0), self.cfg.hidden], torch.bfloat16))
         out, _, _ = buf.combine(y_recv, handle)
         return out
@@ -215,7 +233,8 @@ class MoELayer(nn.Module):
         R, L = buf.group_size, self.num_local_experts
         M = num_max_tokens or x.size(0)
         N, H, I = R * M, cfg.hidden, cfg.intermediate
-        (px, ps), cnt, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, M, cfg.num_experts, use_fp8=True)
+        mx = getattr(self, "_mx", None) if N % 128 == 0 else None  # scale atoms cover whole 128-row tiles
+        (px, ps), cnt, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, M, cfg.num_experts, use_fp8=True, round_scale=mx is not None)
         ws = self.__dict__.setdefault("_ll_ws", {})
         key = (M, x.device)
         if key not in ws:
@@ -227,10 +246,16 @@ class MoELayer(nn.Module):
         w_ = ws[key]
         ends = w_["starts"][:L] + cnt
         a, a_s = px.view(L * N, H), ps.view(L * N, H // 128)
-        gg.grouped_gemm(a, w13, w_["starts"], swiglu=True, a_scales=a_s, b_scales=s13, out=w_["h"], m_ends=ends)
-        C.per_token_cast_to_fp8(w_["h"], False, False, cnt, N, w_["hq"], w_["hs"])
         y = buf.get_next_low_latency_combine_buffer(handle)
-        gg.grouped_gemm(w_["hq"], w2, w_["starts"], a_scales=w_["hs"], b_scales=s2, out=y.view(L * N, H), m_ends=ends)
+        if mx is not None:
+            gg.grouped_gemm(a, w13, w_["starts"], swiglu=True, out=w_["h"], m_ends=ends, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[0])
+            C.per_token_cast_to_fp8(w_["h"], True, False, cnt, N, w_["hq"], w_["hs"])
+            gg.grouped_gemm(w_["hq"], w2, w_["starts"], out=y.view(L * N, H), m_ends=ends, sfa_atoms=gg.build_sf_atoms_a(w_["hs"]),
+                            sfb_atoms=mx[1])
+        else:
+            gg.grouped_gemm(a, w13, w_["starts"], swiglu=True, a_scales=a_s, b_scales=s13, out=w_["h"], m_ends=ends)
+            C.per_token_cast_to_fp8(w_["h"], False, False, cnt, N, w_["hq"], w_["hs"])
+            gg.grouped_gemm(w_["hq"], w2, w_["starts"], a_scales=w_["hs"], b_scales=s2, out=y.view(L * N, H), m_ends=ends)
         out, _, _ = buf.low_latency_combine(y, topk_idx, topk_weights, handle, zero_copy=True)
         return out
 

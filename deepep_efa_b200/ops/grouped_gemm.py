@@ -22,13 +22,29 @@ from .. import _ext
 
 def grouped_gemm(a: torch.Tensor, b: torch.Tensor, m_offsets: torch.Tensor, *, swiglu: bool = False,
                  a_scales: Optional[torch.Tensor] = None, b_scales: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None, num_sms: int = 0, m_ends: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, num_sms: int = 0, m_ends: Optional[torch.Tensor] = None,
+                 sfa_atoms: Optional[torch.Tensor] = None, sfb_atoms: Optional[torch.Tensor] = None) -> torch.Tensor:
     """M-grouped GEMM; see the module docstring. Returns bf16 ``[M, N]`` (``[M, N/2]`` with ``swiglu``).
 
     ``m_ends`` (int32 ``[G]``, optional) makes group g cover rows ``[m_offsets[g], m_ends[g])``: the "masked" form for the
     low-latency layout ``[L, N, hidden]``, where every expert starts at ``g * N`` and only ``packed_recv_count[g]`` rows
-    are valid. Rows of a partly filled last tile are computed and written too (they are padding by contract)."""
-    return _ext.load().grouped_gemm(a, b, m_offsets, 0, swiglu, a_scales, b_scales, out, num_sms, 2000.0, m_ends)
+    are valid; rows past ``m_ends[g]`` are never written.
+
+    ``sfa_atoms`` / ``sfb_atoms`` (from :func:`build_sf_atoms_a` / :func:`build_sf_atoms_b`) select the natively block-scaled
+    FP8 kernel: power-of-two scales are applied by the tensor core (``kind::mxf8f6f4.block_scale``) and a whole tile
+    accumulates in TMEM. Every group must then start on a multiple of 128 rows."""
+    return _ext.load().grouped_gemm(a, b, m_offsets, 0, swiglu, a_scales, b_scales, out, num_sms, 2000.0, m_ends, sfa_atoms, sfb_atoms)
+
+
+def build_sf_atoms_a(a_scales: torch.Tensor) -> torch.Tensor:
+    """UE8M0 scale atoms of the activations for the natively block-scaled FP8 GEMM (``a_scales`` f32 ``[M, K/128]``, powers
+    of two, e.g. from a cast with ``round_scale=True``)."""
+    return _ext.load().build_sf_atoms_a(a_scales.contiguous())
+
+
+def build_sf_atoms_b(b_scales: torch.Tensor, n: int, swiglu: bool = False) -> torch.Tensor:
+    """UE8M0 scale atoms of the weights (``b_scales`` f32 ``[G, N/128, K/128]``, powers of two); built once per weight."""
+    return _ext.load().build_sf_atoms_b(b_scales.contiguous(), n, swiglu)
 
 
 def grouped_gemm_wgrad(a_t: torch.Tensor, b_t: torch.Tensor, m_offsets: torch.Tensor, *, out: Optional[torch.Tensor] = None,

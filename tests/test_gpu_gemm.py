@@ -166,3 +166,30 @@ def test_rowdot_kernel():
     got = _ext.load().rowdot(a, b, pos)
     want = torch.where(pos >= 0, (a[pos.clamp(min=0).long()].float() * b.float().unsqueeze(1)).sum(-1), torch.zeros(N, K, device="cuda"))
     assert torch.allclose(got, want, rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_fp8_native_block_scaling(swiglu):
+    """tcgen05 block-scaled MMA with UE8M0 scale atoms against the dequantised fp32 reference; the row scales differ by
+    powers of two from row to row so that a wrong row-to-scale mapping cannot pass."""
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import build_sf_atoms_a, build_sf_atoms_b, grouped_gemm, reference_grouped_gemm
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(11)
+    rows, K = [128, 256, 0, 384], 512
+    N = 512
+    G, M = len(rows), sum(rows)
+    x = torch.randn(M, K, device="cuda") * torch.pow(2.0, (torch.arange(M, device="cuda") % 7).float()).unsqueeze(1)
+    x = x * torch.pow(2.0, (torch.arange(K, device="cuda") // 128 % 3).float()).unsqueeze(0)
+    a, a_s = C.per_token_cast_to_fp8(x.to(torch.bfloat16), True, False)  # power-of-two scales
+    w = torch.randn(G, N, K, device="cuda") * 0.1 * torch.pow(2.0, (torch.arange(N, device="cuda") // 128 % 4).float()).view(1, N, 1)
+    wb = w.view(G, N // 128, 128, K // 128, 128)
+    b_s = torch.exp2(torch.ceil(torch.log2(wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0))).contiguous()
+    b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous()
+    offs = _offsets(rows)
+    c = grouped_gemm(a, b, offs, swiglu=swiglu, sfa_atoms=build_sf_atoms_a(a_s), sfb_atoms=build_sf_atoms_b(b_s, N, swiglu))
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    ref = reference_grouped_gemm(a, b, offs, swiglu=swiglu, a_scales=a_s, b_scales=b_s)
+    assert _rel_err(c, ref) < (1.5e-2 if swiglu else 1e-2), _rel_err(c, ref)

@@ -76,6 +76,13 @@ def test_moe_layer_forward_backward_gpu():
         torch.cuda.synchronize()
         buf.check_status()
         assert _rel(y8, ref.detach()) < 8e-2, _rel(y8, ref.detach())
+        # the same path with power-of-two scales consumed by the tensor core itself (UE8M0 block scaling)
+        layer.prepare_fp8(native_block_scaling=True)
+        y8n = layer.forward_fp8(x.detach(), idx, w.detach())
+        torch.cuda.synchronize()
+        buf.check_status()
+        assert ep._ext.load().gemm_error(0) == 0
+        assert _rel(y8n, ref.detach()) < 8e-2, _rel(y8n, ref.detach())
     finally:
         vc.destroy()
 
@@ -85,7 +92,7 @@ def test_moe_low_latency_decode_path():
     from deepep_efa_b200.models.moe import MoEConfig, MoELayer, dense_reference
     from deepep_efa_b200.parallel.virtual import VirtualCluster
     T, H, I, E, K = 48, 512, 256, 8, 2
-    vc = VirtualCluster(1, num_nvl_bytes=8 << 20, num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(64, H, 1, E))
+    vc = VirtualCluster(1, num_nvl_bytes=8 << 20, num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(128, H, 1, E))
     try:
         buf = vc.buffers[0]
         layer = MoELayer(MoEConfig(hidden=H, intermediate=I, num_experts=E, num_topk=K, init_std=0.05), buf)
@@ -94,6 +101,14 @@ def test_moe_low_latency_decode_path():
         ref = dense_reference(x, idx, w.masked_fill(idx == -1, 0), layer.w13.detach().float(), layer.w2.detach().float())
         for _ in range(3):  # both parities, workspace reuse
             y = layer.forward_low_latency(x, idx, w, num_max_tokens=64)
+            torch.cuda.synchronize()
+            buf.check_status()
+            assert ep._ext.load().gemm_error(0) == 0
+            assert _rel(y, ref) < 8e-2, _rel(y, ref)
+        # tile-aligned landing zone (N = 128): power-of-two scales applied by the tensor core itself
+        layer.prepare_fp8(native_block_scaling=True)
+        for _ in range(2):
+            y = layer.forward_low_latency(x, idx, w, num_max_tokens=128)
             torch.cuda.synchronize()
             buf.check_status()
             assert ep._ext.load().gemm_error(0) == 0

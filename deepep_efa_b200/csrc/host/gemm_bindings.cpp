@@ -95,11 +95,12 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
             // native block scaling: pre-built UE8M0 atoms (build_sf_atoms_a / build_sf_atoms_b)
             DXG_CHECK(sfb_atoms.has_value(), "sfa_atoms and sfb_atoms go together");
             DXG_CHECK(K % 128 == 0 && N % 128 == 0, "native block scaling needs K % 128 == 0 and N % 128 == 0");
-            const int64_t tiles_n = swiglu ? (N / 2) / 64 : N / 128;
+            DXG_CHECK(!swiglu || (N / 2) % 128 == 0, "native block scaling with swiglu needs N/2 % 128 == 0");
+            const int64_t atoms_n = N / 128;  // plain: one atom per 128-row tile; swiglu: two atoms per 256-row tile
             DXG_CHECK(sfa_atoms->is_cuda() && sfa_atoms->scalar_type() == torch::kUInt8 && sfa_atoms->is_contiguous() &&
                           sfa_atoms->numel() == ((M + 127) / 128) * (K / 128) * 512, "sfa_atoms must be uint8 [ceil(M/128), K/128, 512]");
             DXG_CHECK(sfb_atoms->is_cuda() && sfb_atoms->scalar_type() == torch::kUInt8 && sfb_atoms->is_contiguous() &&
-                          sfb_atoms->numel() == (int64_t)G * tiles_n * (K / 128) * 512, "sfb_atoms must be uint8 [G, n tiles, K/128, 512]");
+                          sfb_atoms->numel() == (int64_t)G * atoms_n * (K / 128) * 512, "sfb_atoms must be uint8 [G, N/128 atoms, K/128, 512]");
             p.sfa_atoms = sfa_atoms->data_ptr<uint8_t>();
             p.sfb_atoms = sfb_atoms->data_ptr<uint8_t>();
         } else if (fp8) {
@@ -275,8 +276,9 @@ torch::Tensor build_sf_atoms_b(const torch::Tensor& scales, int64_t n, bool swig
               "scales must be contiguous CUDA f32 [G, N/128, K/128]");
     c10::cuda::CUDAGuard guard(scales.device());
     const int64_t G = scales.size(0), nkb = scales.size(2);
-    const int64_t tiles = swiglu ? (n / 2) / 64 : n / 128;
-    auto atoms = torch::empty({G, tiles, nkb, 512}, scales.options().dtype(torch::kUInt8));
+    DXG_CHECK(!swiglu || (n / 2) % 128 == 0, "build_sf_atoms_b: swiglu needs N/2 % 128 == 0");
+    const int64_t tiles = swiglu ? (n / 2) / 128 : n / 128;
+    auto atoms = torch::empty({G, tiles, nkb, swiglu ? 1024 : 512}, scales.options().dtype(torch::kUInt8));
     const cudaError_t e = dx::launch_build_sfb_atoms(scales.data_ptr<float>(), atoms.data_ptr<uint8_t>(), (int)G, (int)n, (int)nkb, swiglu ? 1 : 0,
                                                      at::cuda::getCurrentCUDAStream(scales.get_device()).stream());
     DXG_CHECK(e == cudaSuccess, "build_sf_atoms_b: N (and N/2 with swiglu) must be a multiple of 128");

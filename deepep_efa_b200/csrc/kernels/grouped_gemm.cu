@@ -281,17 +281,23 @@ struct TileInfo {
 template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
 struct Cfg {
     static constexpr bool kPromote = kFp8 && !kMx;  // FP8 with fp32 scales: every K block is promoted on the CUDA cores
-    static constexpr int kSfBytes = kMx ? 1024 : 0; // per stage: one 512-byte scale atom for A and one for B
+    static constexpr int kSfBAtoms = kBlockN / 128;                  // 512-byte scale atoms of the B tile
+    static constexpr int kSfTxBytes = kMx ? 512 * (1 + kSfBAtoms) : 0;   // per stage: scale atoms of A and of B
+    static constexpr int kSfBytes = (kSfTxBytes + 1023) / 1024 * 1024;   // stages stay 1024-byte aligned (swizzle atoms)
     // B rows staged per CTA: a CTA pair splits the tile's N between its two CTAs
     static constexpr int kBRows = kPair ? kBlockN / 2 : kBlockN;
     static constexpr int kBTileBytes = kBRows * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes + kSfBytes;
-    static constexpr int kStages = kMx ? 6 : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
+    static constexpr int kStageTxBytes = kATileBytes + kBTileBytes + kSfTxBytes;  // bytes the copies of one stage deliver
+    static constexpr int kStages = kMx ? (kBlockN == 256 ? 4 : 6) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
     static constexpr int kTileRows = kPair ? 2 * kBlockM : kBlockM;  // rows of one scheduled tile (both CTAs of a pair)
     // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
     // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
-    static constexpr int kWindows = kPromote ? 4 : 2;
-    static constexpr int kSfCol0 = kWindows * kBlockN;   // kMx: two alternating sets of (4 columns A + 4 columns B) after the windows
+    // kMx with 256-column tiles: ONE window (two would fill TMEM and leave no room for the scale columns); the epilogue of
+    // that variant drains the accumulator into registers first and releases the window before it stores.
+    static constexpr int kWindows = kPromote ? 4 : ((kMx && kBlockN == 256) ? 1 : 2);
+    static constexpr int kSfCol0 = kWindows * kBlockN;   // kMx: two alternating sets of (4 columns A + 4 per B atom) after the windows
+    static constexpr int kSfColsPerBuf = 4 + 4 * kSfBAtoms;
     static constexpr int kTmemCols = kMx ? 512 : kWindows * kBlockN;
     static constexpr int kOutCols = kSwiGLU ? kBlockN / 2 : kBlockN;
     // FP8 promotes every K block on the CUDA cores, so it gets two epilogue warps per TMEM lane quarter (each takes half
@@ -307,7 +313,8 @@ template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
 __global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
     using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
-    static_assert(!kMx || (kFp8 && !kPair && kBlockN == 128), "native block scaling: e4m3 operands, single CTA, 128-column tiles");
+    static_assert(!kMx || (kFp8 && !kPair && (kBlockN == 128 || (kBlockN == 256 && kSwiGLU))),
+                  "native block scaling: e4m3 operands, single CTA, 128-column tiles (256 with SwiGLU)");
     const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader (issues the MMAs of the pair)
     const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -456,14 +463,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         continue;
                     }
-                    mbar_expect_tx(&full[stage], C::kStageBytes);
+                    mbar_expect_tx(&full[stage], C::kStageTxBytes);
                     if constexpr (kMx) {
                         // scale atoms: [row tile][K block][512] for A, [group][n tile][K block][512] for B
                         uint8_t* ssf = sb + C::kBTileBytes;
                         const size_t nkb = (size_t)(p.k / 128);
                         bulk_load_1d(ssf, p.sfa_atoms + ((size_t)(ti.a_row >> 7) * nkb + kb) * 512, 512, &full[stage]);
-                        bulk_load_1d(ssf + 512, p.sfb_atoms + (((size_t)ti.group * (p.n / kBlockN) + ti.nt) * nkb + kb) * 512, 512,
-                                     &full[stage]);
+                        bulk_load_1d(ssf + 512, p.sfb_atoms + (((size_t)ti.group * (p.n / kBlockN) + ti.nt) * nkb + kb) * (512 * C::kSfBAtoms),
+                                     512 * C::kSfBAtoms, &full[stage]);
                     }
                     tma_load_2d(&map_a, &full[stage], sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
                     if (kSwiGLU) {
@@ -524,9 +531,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if constexpr (kMx) {
                         // scale atoms of this stage -> TMEM (alternating column sets), then four K=32 MMAs that read them
                         const uint32_t ssf = sb + C::kBTileBytes;
-                        const uint32_t t_sfa = tmem_base + (uint32_t)(C::kSfCol0 + sf_buf * 8), t_sfb = t_sfa + 4;
+                        const uint32_t t_sfa = tmem_base + (uint32_t)(C::kSfCol0 + sf_buf * C::kSfColsPerBuf), t_sfb = t_sfa + 4;
                         tmem_cp_sf(t_sfa, make_sf_desc(ssf));
-                        tmem_cp_sf(t_sfb, make_sf_desc(ssf + 512));
+#pragma unroll
+                        for (int at = 0; at < C::kSfBAtoms; ++at) tmem_cp_sf(t_sfb + 4 * at, make_sf_desc(ssf + 512 + 512 * at));
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             umma_mx(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, t_sfa, t_sfb,
@@ -679,7 +687,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
                 __nv_bfloat16* wbase = cbase + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
                 const int rows_valid = min(32, ti.c_row_end - (ti.c_row + q * 32));
-                if constexpr (kSwiGLU) {
+                if constexpr (kSwiGLU && C::kWindows == 1) {
+                    // single window: the accumulator goes to registers (as BF16 outputs) first, the window returns to the MMA
+                    // issuer, and only then the stores run
+                    int4 keep[C::kOutCols / 32][4];
+#pragma unroll
+                    for (int ci = 0; ci < C::kOutCols / 32; ++ci) {
+                        uint32_t v[32], u[32];
+                        tmem_ld32(taddr + ci * 32, v);
+                        tmem_ld32(taddr + kBlockN / 2 + ci * 32, u);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float o[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) o[j] = silu(__uint_as_float(v[i + j])) * __uint_as_float(u[i + j]);
+                            keep[ci][i / 8] = pack8_bf16(o);
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) release_window(&tmem_empty[win]);
+#pragma unroll
+                    for (int ci = 0; ci < C::kOutCols / 32; ++ci) store_block_coalesced<32>(out_stage, keep[ci], wbase + ci * 32, ldc, rows_valid, lane);
+                    win_phase ^= 1;  // kWindows == 1: the same window, next phase
+                    continue;
+                } else if constexpr (kSwiGLU) {
 #pragma unroll 1
                     for (int c = 0; c < C::kOutCols; c += 32) {
                         uint32_t v[32], u[32];
@@ -834,7 +867,10 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
         if (a.fp8 && a.sfa_atoms != nullptr) {
             // native block scaling: pre-built UE8M0 scale atoms, every group starts on a multiple of 128 rows
             if (a.sfb_atoms == nullptr || a.k % 128 != 0 || a.n % 128 != 0) return cudaErrorInvalidValue;
-            if (a.swiglu) return launch_impl<128, true, true, false, true>(a, stream);
+            if (a.swiglu) {
+                if ((a.n / 2) % 128 != 0) return cudaErrorInvalidValue;  // tiles of 128 gate + 128 up columns
+                return launch_impl<256, true, true, false, true>(a, stream);
+            }
             return launch_impl<128, true, false, false, true>(a, stream);
         }
         if (a.fp8) {

@@ -7,8 +7,9 @@
 //
 // These kernels turn fp32 power-of-two scales into atoms:
 //   A: scales [M, K/128]          -> [ceil(M/128)][K/128][512]
-//   B: scales [G, N/128, K/128]   -> [G][tiles][K/128][512], tiles of 128 B rows; with SwiGLU a tile is 64 gate rows followed by
-//                                    the 64 matching up rows, so its atom mixes the two scale blocks (m1 = 0,1 gate; 2,3 up)
+//   B: scales [G, N/128, K/128]   -> plain: [G][N/128][K/128][512], tiles of 128 B rows;
+//                                    SwiGLU: [G][N/256][K/128][2][512], a tile is 128 gate rows followed by the 128 matching up
+//                                    rows: first atom = the gate rows' scale block, second atom = the up rows' block
 // The reference has no counterpart (no GEMM).
 #include "gemm_api.h"
 
@@ -47,18 +48,15 @@ __global__ void sfb_atoms_kernel(const float* __restrict__ scales, uint8_t* __re
         const long long gt = tk / num_kb;
         const int t = (int)(gt % tiles);
         const long long g = gt / tiles;
-        uint32_t w[4];
         if (swiglu) {
-            const int gate_block = (t * 64) / 128, up_block = (n / 2 + t * 64) / 128;
-            const uint32_t wg = ue8m0_word(scales[(g * nb + gate_block) * num_kb + kb]);
-            const uint32_t wu = ue8m0_word(scales[(g * nb + up_block) * num_kb + kb]);
-            w[0] = w[1] = wg;
-            w[2] = w[3] = wu;
+            const uint32_t wg = ue8m0_word(scales[(g * nb + t) * num_kb + kb]);
+            const uint32_t wu = ue8m0_word(scales[(g * nb + nb / 2 + t) * num_kb + kb]);
+            *reinterpret_cast<uint4*>(atoms + tk * 1024 + m0 * 16) = make_uint4(wg, wg, wg, wg);
+            *reinterpret_cast<uint4*>(atoms + tk * 1024 + 512 + m0 * 16) = make_uint4(wu, wu, wu, wu);
         } else {
             const uint32_t wv = ue8m0_word(scales[(g * nb + t) * num_kb + kb]);
-            w[0] = w[1] = w[2] = w[3] = wv;
+            *reinterpret_cast<uint4*>(atoms + tk * 512 + m0 * 16) = make_uint4(wv, wv, wv, wv);
         }
-        *reinterpret_cast<uint4*>(atoms + tk * 512 + m0 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -75,7 +73,7 @@ cudaError_t launch_build_sfa_atoms(const float* scales, uint8_t* atoms, int rows
 
 cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, cudaStream_t stream) {
     if (n % 128 != 0 || (swiglu && (n / 2) % 128 != 0)) return cudaErrorInvalidValue;
-    const int tiles = swiglu ? (n / 2) / 64 : n / 128;
+    const int tiles = swiglu ? (n / 2) / 128 : n / 128;
     const long long total = (long long)groups * tiles * num_kb * 32;
     if (total <= 0) return cudaSuccess;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);

@@ -31,6 +31,7 @@ struct GroupedGemmArgs {
     // when sfa_atoms is set the fp32 scale pointers are ignored
     const uint8_t* sfa_atoms;
     const uint8_t* sfb_atoms;
+    int mx_wide;              // swiglu only: 1 = 256-column tiles (one accumulator window; large groups), 0 = 128-column tiles
     const int* m_offsets;     // [G+1] device memory
     const int* m_ends;        // optional [G]: group g covers rows [m_offsets[g], m_ends[g]) instead of up to m_offsets[g+1]
                               // (mode 0 only; the low-latency layout has fixed group starts and a count per expert)
@@ -76,6 +77,7 @@ cudaError_t launch_rowdot(const void* a, const void* b, const int* pos, float* o
 
 // Scale atoms of the natively block-scaled FP8 GEMM (sf_atoms.cu); scales must be powers of two.
 cudaError_t launch_build_sfa_atoms(const float* scales, uint8_t* atoms, int rows, int num_kb, cudaStream_t stream);
-cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, cudaStream_t stream);
+cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, int wide,
+                                   cudaStream_t stream);
 
 }  // namespace dx

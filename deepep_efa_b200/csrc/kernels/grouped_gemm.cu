@@ -868,8 +868,9 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
             // native block scaling: pre-built UE8M0 scale atoms, every group starts on a multiple of 128 rows
             if (a.sfb_atoms == nullptr || a.k % 128 != 0 || a.n % 128 != 0) return cudaErrorInvalidValue;
             if (a.swiglu) {
-                if ((a.n / 2) % 128 != 0) return cudaErrorInvalidValue;  // tiles of 128 gate + 128 up columns
-                return launch_impl<256, true, true, false, true>(a, stream);
+                if ((a.n / 2) % 128 != 0) return cudaErrorInvalidValue;  // gate/up halves start on scale-block boundaries
+                if (a.mx_wide) return launch_impl<256, true, true, false, true>(a, stream);
+                return launch_impl<128, true, true, false, true>(a, stream);
             }
             return launch_impl<128, true, false, false, true>(a, stream);
         }

@@ -8,8 +8,9 @@
 // These kernels turn fp32 power-of-two scales into atoms:
 //   A: scales [M, K/128]          -> [ceil(M/128)][K/128][512]
 //   B: scales [G, N/128, K/128]   -> plain: [G][N/128][K/128][512], tiles of 128 B rows;
-//                                    SwiGLU: [G][N/256][K/128][2][512], a tile is 128 gate rows followed by the 128 matching up
-//                                    rows: first atom = the gate rows' scale block, second atom = the up rows' block
+//                                    SwiGLU, 256-column tiles (wide): [G][N/256][K/128][2][512], a tile is 128 gate rows followed
+//                                    by the 128 matching up rows: first atom = the gate rows' scale block, second = the up rows'
+//                                    SwiGLU, 128-column tiles: [G][N/128][K/128][512], 64 gate + 64 up rows share one atom
 // The reference has no counterpart (no GEMM).
 #include "gemm_api.h"
 
@@ -39,7 +40,7 @@ __global__ void sfa_atoms_kernel(const float* __restrict__ scales, uint8_t* __re
 }
 
 __global__ void sfb_atoms_kernel(const float* __restrict__ scales, uint8_t* __restrict__ atoms, int n, int num_kb, int tiles, int swiglu,
-                                 long long total) {
+                                 int wide, long long total) {
     const int nb = n / 128;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int m0 = (int)(i & 31);
@@ -48,7 +49,13 @@ __global__ void sfb_atoms_kernel(const float* __restrict__ scales, uint8_t* __re
         const long long gt = tk / num_kb;
         const int t = (int)(gt % tiles);
         const long long g = gt / tiles;
-        if (swiglu) {
+        if (swiglu && wide == 0) {
+            // 128-column tiles: 64 gate rows then the 64 matching up rows share one atom (m1 = 0,1 gate; 2,3 up)
+            const int gate_block = (t * 64) / 128, up_block = (n / 2 + t * 64) / 128;
+            const uint32_t wg = ue8m0_word(scales[(g * nb + gate_block) * num_kb + kb]);
+            const uint32_t wu = ue8m0_word(scales[(g * nb + up_block) * num_kb + kb]);
+            *reinterpret_cast<uint4*>(atoms + tk * 512 + m0 * 16) = make_uint4(wg, wg, wu, wu);
+        } else if (swiglu) {
             const uint32_t wg = ue8m0_word(scales[(g * nb + t) * num_kb + kb]);
             const uint32_t wu = ue8m0_word(scales[(g * nb + nb / 2 + t) * num_kb + kb]);
             *reinterpret_cast<uint4*>(atoms + tk * 1024 + m0 * 16) = make_uint4(wg, wg, wg, wg);
@@ -71,13 +78,14 @@ cudaError_t launch_build_sfa_atoms(const float* scales, uint8_t* atoms, int rows
     return cudaGetLastError();
 }
 
-cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, cudaStream_t stream) {
+cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, int wide,
+                                   cudaStream_t stream) {
     if (n % 128 != 0 || (swiglu && (n / 2) % 128 != 0)) return cudaErrorInvalidValue;
-    const int tiles = swiglu ? (n / 2) / 128 : n / 128;
+    const int tiles = swiglu ? (wide ? (n / 2) / 128 : (n / 2) / 64) : n / 128;
     const long long total = (long long)groups * tiles * num_kb * 32;
     if (total <= 0) return cudaSuccess;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    sfb_atoms_kernel<<<blocks, 256, 0, stream>>>(scales, atoms, n, num_kb, tiles, swiglu, total);
+    sfb_atoms_kernel<<<blocks, 256, 0, stream>>>(scales, atoms, n, num_kb, tiles, swiglu, wide, total);
     return cudaGetLastError();
 }
 

@@ -179,7 +179,10 @@ class MoELayer(nn.Module):
         self._fp8 = (q(self.w13), q(self.w2))
         if native_block_scaling:
             (_, s13), (_, s2) = self._fp8
-            self._mx = (gg.build_sf_atoms_b(s13, self.w13.size(1), swiglu=True), gg.build_sf_atoms_b(s2, self.w2.size(1)))
+            n13 = self.w13.size(1)
+            # (wide tiles for large groups, narrow tiles for small groups / decode, second GEMM)
+            self._mx = (gg.build_sf_atoms_b(s13, n13, swiglu=True, wide=True), gg.build_sf_atoms_b(s2, self.w2.size(1)),
+                        gg.build_sf_atoms_b(s13, n13, swiglu=True, wide=False))
 
     @torch.no_grad()
     def forward_fp8(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -202,7 +205,8 @@ class MoELayer(nn.Module):
         a_s = gather_rows(rs, plan.src_row) if rs.size(1) % 4 == 0 else rs.index_select(0, plan.src_row.clamp(min=0).long())
         if mx is not None:
             # padding rows of the plan carry all-zero data; whatever exponent their zero scale maps to does not matter
-            h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[0])
+            wide = plan.num_rows >= 512 * self.num_local_experts
+            h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[0 if wide else 2])
             hq, hs = C.per_token_cast_to_fp8(h, True, False)
             y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, sfa_atoms=gg.build_sf_atoms_a(hs), sfb_atoms=mx[1])
         else:
@@ -248,7 +252,7 @@ class MoELayer(nn.Module):
         a, a_s = px.view(L * N, H), ps.view(L * N, H // 128)
         y = buf.get_next_low_latency_combine_buffer(handle)
         if mx is not None:
-            gg.grouped_gemm(a, w13, w_["starts"], swiglu=True, out=w_["h"], m_ends=ends, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[0])
+            gg.grouped_gemm(a, w13, w_["starts"], swiglu=True, out=w_["h"], m_ends=ends, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[2])
             C.per_token_cast_to_fp8(w_["h"], True, False, cnt, N, w_["hq"], w_["hs"])
             gg.grouped_gemm(w_["hq"], w2, w_["starts"], out=y.view(L * N, H), m_ends=ends, sfa_atoms=gg.build_sf_atoms_a(w_["hs"]),
                             sfb_atoms=mx[1])

@@ -168,8 +168,8 @@ def test_rowdot_kernel():
     assert torch.allclose(got, want, rtol=1e-3, atol=1e-2)
 
 
-@pytest.mark.parametrize("swiglu", [False, True])
-def test_fp8_native_block_scaling(swiglu):
+@pytest.mark.parametrize("swiglu,wide", [(False, True), (True, True), (True, False)])
+def test_fp8_native_block_scaling(swiglu, wide):
     """tcgen05 block-scaled MMA with UE8M0 scale atoms against the dequantised fp32 reference; the row scales differ by
     powers of two from row to row so that a wrong row-to-scale mapping cannot pass."""
     from deepep_efa_b200 import _ext
@@ -188,7 +188,7 @@ def test_fp8_native_block_scaling(swiglu):
     b_s = torch.exp2(torch.ceil(torch.log2(wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0))).contiguous()
     b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous()
     offs = _offsets(rows)
-    c = grouped_gemm(a, b, offs, swiglu=swiglu, sfa_atoms=build_sf_atoms_a(a_s), sfb_atoms=build_sf_atoms_b(b_s, N, swiglu))
+    c = grouped_gemm(a, b, offs, swiglu=swiglu, sfa_atoms=build_sf_atoms_a(a_s), sfb_atoms=build_sf_atoms_b(b_s, N, swiglu, wide))
     torch.cuda.synchronize()
     assert C.gemm_error(0) == 0
     ref = reference_grouped_gemm(a, b, offs, swiglu=swiglu, a_scales=a_s, b_scales=b_s)

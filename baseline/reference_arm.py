@@ -76,8 +76,8 @@ def main(args) -> None:
               "data": "synthetic: N(0,1) bf16 activations, uniform top-8 of 256 experts without replacement, softmax weights",
               "config": {"model": "low-latency EP dispatch+combine", "tokens_per_rank": T, "global_batch": T * world, "seq_len": 1,
                          "hidden": H, "num_experts": E, "topk": K, "parallelism": f"ep{world}", "l2": "256 MB flush between timed iterations",
-                         "timing": "CUDA events per iteration, max over ranks",
-                         "path": "reference low_latency_dispatch/combine, single-node NCCL fallback (deep_ep/buffer.py:2265-2303)"}}
+                         "timing": "CUDA events per iteration, max over ranks"},
+              "path": "reference low_latency_dispatch/combine, single-node NCCL fallback (deep_ep/buffer.py:2265-2303)"}
 
     def ll_step():
         _, _, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, T, E, use_fp8=True, topk_weights=topk_w)

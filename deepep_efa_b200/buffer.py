@@ -59,6 +59,8 @@ class Buffer:
     """
 
     num_sms: int = 32
+    # CTAs of the low-latency kernels; None = one CTA per token (+1) for dispatch and every SM for combine
+    ll_num_sms: Optional[int] = None
 
     # ------------------------------------------------------------------------------------------
     # construction / teardown
@@ -93,6 +95,10 @@ class Buffer:
         self._virtual_peers: Optional[List["Buffer"]] = None
         self._hier = None
         self._ll_mask_local = None
+        if allow_mnnvl or use_fabric:
+            # fabric / multi-node NVLink handles are not built: peers are mapped with plain CUDA IPC, which covers one box
+            _log(_logging.WARNING, group.rank() if group is not None else 0,
+                 "allow_mnnvl / use_fabric are ignored: this library maps peers with CUDA IPC inside one NVSwitch domain")
 
         if _virtual is not None:
             self.rank, self.group_size = _virtual
@@ -197,6 +203,14 @@ class Buffer:
         Buffer.num_sms = int(new_num_sms)
 
     @staticmethod
+    def set_low_latency_num_sms(new_num_sms: Optional[int]) -> None:
+        """Bound the grid of the low-latency kernels (``None`` restores the default: one CTA per token for dispatch,
+        every SM for combine). With the receive hook this leaves the remaining SMs to a GEMM that runs between the two
+        halves; the kernels stride over tokens, so any value >= 2 is valid."""
+        assert new_num_sms is None or new_num_sms >= 2
+        Buffer.ll_num_sms = None if new_num_sms is None else int(new_num_sms)
+
+    @staticmethod
     def capture() -> EventOverlap:
         """An event recorded on the current stream (deep_ep/buffer.py:294-302)."""
         return EventOverlap(EventHandle())
@@ -296,6 +310,15 @@ class Buffer:
             torch.cuda.synchronize()
         if self.runtime.status_code() != 0:
             raise EPTimeoutError(self.runtime.status_string())
+        if sync:
+            # the grouped GEMM reports through a per-device word (1 = a bounded pipeline wait ran out, 2 = a group of the
+            # natively block-scaled kernel does not start on a 128-row boundary); reading it synchronises, so it is only
+            # looked at here
+            err = self._C.gemm_error(self.device.index)
+            if err != 0:
+                self._C.gemm_clear_error(self.device.index)
+                raise EPTimeoutError(f"grouped GEMM reported error {err} " +
+                                     ("(pipeline wait timed out)" if err == 1 else "(group start not on a 128-row boundary)"))
 
     def recover(self) -> None:
         """Collective reset after an error: zero the control block and all sequence state."""
@@ -455,6 +478,9 @@ class Buffer:
                 combine_src=rt.view(lay["combine_src"][p], [L, N, hidden], torch.bfloat16),
                 count=torch.zeros(L, dtype=torch.int32, device=self.device),
                 layout_range=torch.zeros(L, R, dtype=torch.int64, device=self.device),
+                # row of every (token, k) selection at its expert's rank, written by dispatch and read by the pull form of
+                # combine; lives as long as the handle's tensors (until the second next dispatch)
+                send_row=torch.full((num_max_tokens * 32,), -1, dtype=torch.int32, device=self.device),
             )
             v.append(d)
         self._ll_cache[key] = v
@@ -834,6 +860,8 @@ def _ll_stream_exit(buf: Buffer, ctx, tensors) -> EventOverlap:
 
 def _ll_num_sms(num_tokens: int, num_virtual: int) -> int:
     cap = _NUM_SM_B200 if num_virtual == 1 else _NUM_SM_B200 // num_virtual
+    if Buffer.ll_num_sms is not None:
+        cap = min(cap, Buffer.ll_num_sms)
     return max(2, min(num_tokens + 1, cap))
 
 
@@ -849,7 +877,7 @@ def _ll_dispatch_many(bufs: List[Buffer], calls, num_max_tokens: int, num_expert
     hidden = calls[0][0].size(1)
     for b, (x, topk_idx, cum, wait) in zip(bufs, calls):
         v = b._ll_views(num_max_tokens, hidden, num_experts)[parity]
-        per_rank.append((x, topk_idx, v["count"], v["layout_range"], cum, wait, None))
+        per_rank.append((x, topk_idx, v["count"], v["layout_range"], cum, wait, v["send_row"]))
         if use_fp8:
             rx = (v["x_fp8"], v["scales_ue8m0"] if use_ue8m0 else v["scales"])
         else:
@@ -874,25 +902,34 @@ def _ll_combine_many(bufs: List[Buffer], calls, zero_copy: bool, async_finish: b
     V = len(bufs)
     per_rank, outs = [], []
     parity = None
+    pull, close_barrier = True, False
     for b, (x, topk_idx, topk_w, handle, out, wait) in zip(bufs, calls):
         src_info, layout_range, num_max_tokens, hidden, num_experts = handle
         views = b._ll_views(num_max_tokens, hidden, num_experts)
         parity = _parity_of(views, src_info)
         if zero_copy:
             x = views[parity]["combine_src"]
+        # Expert outputs that already sit in symmetric memory (the zero-copy buffer, or a tensor from empty_symmetric)
+        # are read in place by the home ranks; anything else is pushed through the stage. Every rank of the group must
+        # pass the same kind of tensor: the two forms are different protocols.
+        off = b.runtime.symmetric_offset(x)
+        if off < 0:
+            pull = False
+        elif x.data_ptr() != views[parity]["combine_src"].data_ptr():
+            close_barrier = True  # a caller-owned tensor: its owner may rewrite it as soon as the call returns
         if out is None:
             out = torch.empty((topk_idx.size(0), hidden), dtype=torch.bfloat16, device=topk_idx.device)
-        per_rank.append((x, topk_idx, topk_w, src_info, layout_range, out, wait))
+        per_rank.append((x, topk_idx, topk_w, src_info, layout_range, out, wait, views[parity]["send_row"]))
         outs.append(out)
     _, _, num_max_tokens, hidden, num_experts = calls[0][3]
     num_sms = _ll_num_sms(_NUM_SM_B200, V)
 
     def launch(phases: int):
-        C.ll_combine(rts, per_rank, num_max_tokens, num_experts, parity, phases, num_sms)
+        C.ll_combine(rts, per_rank, num_max_tokens, num_experts, parity, phases, num_sms, pull, close_barrier)
 
     ctx, _ = _ll_stream_enter(bufs[0], async_finish)
     with nvtx_range("ep.ll_combine"):
         launch(1 if return_recv_hook else 3)
-    event = _ll_stream_exit(bufs[0], ctx, [c[0] for c in calls] + outs)
+    event = _ll_stream_exit(bufs[0], ctx, [c[0] for c in calls] + [o for o in outs if o.is_cuda])
     hook = (lambda: launch(2)) if return_recv_hook else None
     return [(o, event, hook) for o in outs]

@@ -16,24 +16,8 @@
 #include "../kernels/gemm_api.h"
 #include "runtime.hpp"
 
-#include <execinfo.h>
-#include <signal.h>
-#include <unistd.h>
-
 namespace py = pybind11;
 using dxh::RuntimeCore;
-
-// Debug aid (DEEPEP_DEBUG_SEGV=1): print the native call stack of a crashing thread before the default
-// action runs, so that a host-side fault in this extension can be located without a debugger.
-static void dx_segv_handler(int sig) {
-    void* frames[64];
-    const int n = backtrace(frames, 64);
-    const char msg[] = "\n[deepep_efa_b200] fatal signal, native backtrace:\n";
-    (void)!write(2, msg, sizeof(msg) - 1);
-    backtrace_symbols_fd(frames, n, 2);
-    signal(sig, SIG_DFL);
-    raise(sig);
-}
 
 namespace {
 
@@ -436,7 +420,7 @@ dx::LLRegion make_region(const dxh::LowLatencyLayout& l) {
     return r;
 }
 
-// Per rank tuple: (x, topk_idx, packed_recv_count, layout_range, cumulative_stats|None, wait_stats|None, send_slot|None)
+// Per rank tuple: (x, topk_idx, packed_recv_count, layout_range, cumulative_stats|None, wait_stats|None, send_row|None)
 void ll_dispatch(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int num_max_tokens, int num_experts, bool use_fp8,
                  bool round_scale, bool use_ue8m0, int parity, int phases, int num_sms) {
     const int V = (int)rts.size();
@@ -455,7 +439,9 @@ void ll_dispatch(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int
         auto wait = opt_tensor(t[5]);
         auto slot = opt_tensor(t[6]);
         const int R = rt->core->num_ranks();
-        DX_CHECK(x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "x must be contiguous bf16 [T,hidden]");
+        DX_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "x must be contiguous bf16 [T,hidden] on the GPU");
+        DX_CHECK(x.device().index() == rt->core->device() && topk_idx.is_cuda() && topk_idx.device() == x.device() && count.is_cuda() && range.is_cuda(),
+                 "low_latency_dispatch: every tensor must live on this rank's GPU");
         const int T = (int)x.size(0), H = (int)x.size(1);
         DX_CHECK(T <= num_max_tokens, "more tokens than num_max_dispatch_tokens_per_rank");
         DX_CHECK(H % 128 == 0 && (!use_ue8m0 || H % 512 == 0), "hidden must be a multiple of 128 (512 with UE8M0)");
@@ -483,15 +469,19 @@ void ll_dispatch(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int
         a.layout_range = range.data_ptr<int64_t>();
         a.cumulative_stats = ptr_or_null<int>(cum);
         a.wait_cost_stats = ptr_or_null<int64_t>(wait);
-        a.send_slot = ptr_or_null<int>(slot);
+        if (slot.has_value())
+            DX_CHECK(slot->is_cuda() && slot->scalar_type() == torch::kInt32 && slot->is_contiguous() && slot->numel() >= (int64_t)T * topk_idx.size(1), "send_row must be int32 [T,K] on the GPU");
+        a.send_row = ptr_or_null<int>(slot);
         a.num_sms = num_sms;
     }
     check_launch(dx::launch_ll_dispatch(args.data(), V, cur_stream(rts[0])), "low_latency_dispatch");
 }
 
-// Per rank tuple: (x, topk_idx, topk_weights, src_info, layout_range, out, wait_stats|None)
+// Per rank tuple: (x, topk_idx, topk_weights, src_info, layout_range, out, wait_stats|None, send_row|None)
+// pull: x of every rank lives in its symmetric buffer and send_row comes from the dispatch of the same handle; the home
+// ranks read the rows in place. close_barrier: readers report back before the kernel ends (x is not the zero-copy buffer).
 void ll_combine(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int num_max_tokens, int num_experts, int parity, int phases,
-                int num_sms) {
+                int num_sms, bool pull, bool close_barrier) {
     const int V = (int)rts.size();
     DX_CHECK(V >= 1 && V <= dx::kMaxVirtualRanks && (int)per_rank.size() == V, "ll_combine: one entry per rank");
     c10::cuda::CUDAGuard guard(rts[0]->core->device());
@@ -499,8 +489,9 @@ void ll_combine(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int 
     for (int v = 0; v < V; ++v) {
         Runtime* rt = rts[v];
         const py::tuple& t = per_rank[v];
-        DX_CHECK(t.size() == 7, "ll_combine: per-rank tuple must have 7 entries");
+        DX_CHECK(t.size() == 8, "ll_combine: per-rank tuple must have 8 entries");
         auto x = t[0].cast<torch::Tensor>();
+        auto send_row = opt_tensor(t[7]);
         auto topk_idx = t[1].cast<torch::Tensor>();
         auto topk_w = t[2].cast<torch::Tensor>();
         auto src_info = t[3].cast<torch::Tensor>();
@@ -509,7 +500,11 @@ void ll_combine(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int 
         auto wait = opt_tensor(t[6]);
         const int R = rt->core->num_ranks();
         const int L = num_experts / R;
-        DX_CHECK(x.dim() == 3 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16 && x.size(0) == L && x.size(1) == (int64_t)R * num_max_tokens, "x must be contiguous bf16 [L, R*max_tokens, hidden]");
+        DX_CHECK(x.is_cuda() && x.dim() == 3 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16 && x.size(0) == L && x.size(1) == (int64_t)R * num_max_tokens, "x must be contiguous bf16 [L, R*max_tokens, hidden] on the GPU");
+        DX_CHECK(x.device().index() == rt->core->device() && topk_idx.is_cuda() && topk_w.is_cuda() && src_info.is_cuda() && range.is_cuda() &&
+                     topk_idx.device() == x.device() && topk_w.device() == x.device(), "low_latency_combine: inputs must live on this rank's GPU");
+        // the result may go to device memory or straight to pinned (page-locked, device-mapped) host memory
+        DX_CHECK((out.is_cuda() && out.device() == x.device()) || (out.device().is_cpu() && out.is_pinned()), "out must be on this rank's GPU or in pinned host memory");
         const int H = (int)x.size(2);
         DX_CHECK(topk_idx.scalar_type() == torch::kInt64 && topk_idx.is_contiguous() && topk_idx.dim() == 2, "topk_idx must be int64 [T,K]");
         const int T = (int)topk_idx.size(0);
@@ -538,6 +533,18 @@ void ll_combine(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int 
         a.num_max_tokens = num_max_tokens;
         a.phases = phases;
         a.num_sms = num_sms;
+        a.pull = pull ? 1 : 0;
+        a.close_barrier = (pull && close_barrier) ? 1 : 0;
+        a.x_off = 0;
+        a.send_row = nullptr;
+        if (pull) {
+            const int64_t xo = rt->symmetric_offset(x);
+            DX_CHECK(xo >= 0 && xo % 16 == 0, "pull combine: x must live in this rank's symmetric buffer");
+            DX_CHECK(send_row.has_value() && send_row->is_cuda() && send_row->scalar_type() == torch::kInt32 && send_row->is_contiguous() &&
+                         send_row->numel() >= (int64_t)T * topk_idx.size(1), "pull combine: send_row must be int32 [T,K] on the GPU");
+            a.x_off = (uint64_t)xo;
+            a.send_row = send_row->data_ptr<int>();
+        }
     }
     check_launch(dx::launch_ll_combine(args.data(), V, cur_stream(rts[0])), "low_latency_combine");
 }
@@ -565,10 +572,6 @@ void bind_hier(py::module_& m);  // hier_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "deepep_efa_b200 native runtime (sm_100a)";
-    if (const char* e = std::getenv("DEEPEP_DEBUG_SEGV"); e != nullptr && e[0] == '1') {
-        signal(SIGSEGV, dx_segv_handler);
-        signal(SIGBUS, dx_segv_handler);
-    }
 
     py::class_<dxh::Config>(m, "Config")
         .def(py::init<int, int, int, int, int>(), py::arg("num_sms") = 32, py::arg("num_max_nvl_chunked_send_tokens") = 6,
@@ -625,6 +628,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("set_timeout_ms", [](Runtime& r, double ms) { r.core->set_timeout_ms(ms); })
         .def("set_debug_checks", [](Runtime& r, bool on) { r.core->set_debug_checks(on); })
         .def("debug_checks", [](Runtime& r) { return r.core->debug_checks(); })
+        .def("set_debug_extent", [](Runtime& r, int64_t bytes) { r.core->set_debug_extent((uint64_t)bytes); })
         .def("timeout_ms", [](Runtime& r) { return r.core->timeout_ms(); })
         .def("status_code", [](Runtime& r) { return r.core->status_code(); })
         .def("status_string", [](Runtime& r) { return r.core->status_string(); })
@@ -653,7 +657,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false, py::arg("use_ue8m0") = false,
           py::arg("group_counts") = py::none(), py::arg("rows_per_group") = 1, py::arg("out_q") = py::none(), py::arg("out_s") = py::none());
     m.def("ll_dispatch", &ll_dispatch);
-    m.def("ll_combine", &ll_combine);
+    m.def("ll_combine", &ll_combine, py::arg("runtimes"), py::arg("per_rank"), py::arg("num_max_tokens"), py::arg("num_experts"),
+          py::arg("parity"), py::arg("phases"), py::arg("num_sms"), py::arg("pull") = false, py::arg("close_barrier") = false);
     m.def("ll_layout", &ll_layout);
     bind_gemm(m);
     bind_hier(m);

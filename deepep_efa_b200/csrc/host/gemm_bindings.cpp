@@ -71,6 +71,12 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     DXG_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "operands must be 16-byte aligned");
     const int G = (int)m_offsets.numel() - 1;
     const int device = a.device().index();
+    // every operand and output is dereferenced by the kernel on A's device: a host tensor or one from another GPU
+    // must be refused here, it would be an illegal address there
+    auto same_dev = [&](const c10::optional<torch::Tensor>& t) { return !t.has_value() || (t->is_cuda() && t->device() == a.device()); };
+    DXG_CHECK(b.device() == a.device() && m_offsets.device() == a.device(), "A, B and m_offsets must live on the same GPU");
+    DXG_CHECK(same_dev(a_scales) && same_dev(b_scales) && same_dev(out) && same_dev(m_ends) && same_dev(sfa_atoms) && same_dev(sfb_atoms),
+              "scales, atoms, m_ends and out must be CUDA tensors on A's device");
     c10::cuda::CUDAGuard guard(device);
     dx::GroupedGemmArgs p{};
     p.num_groups = G;

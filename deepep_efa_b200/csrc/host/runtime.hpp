@@ -109,6 +109,9 @@ class RuntimeCore {
 
     void set_debug_checks(bool on) { debug_checks_ = on; }
     bool debug_checks() const { return debug_checks_; }
+    // Test hook: check row addresses against a smaller extent than the real allocation (0 = the real size), so that a test
+    // can provoke a violation with an address that still lies inside this rank's own buffer.
+    void set_debug_extent(uint64_t bytes) { debug_extent_override_ = bytes; }
 
     void set_timeout_ms(double ms) {
         timeout_ms_ = ms;
@@ -176,7 +179,7 @@ class RuntimeCore {
         c.trace = trace_;
         c.timeout_cycles = timeout_cycles_;
         c.mask_on_timeout = mask_on_timeout_ ? 1 : 0;
-        c.debug_extent = debug_checks_ ? (unsigned long long)total_bytes_ : 0ull;
+        c.debug_extent = debug_checks_ ? (unsigned long long)(debug_extent_override_ != 0 ? debug_extent_override_ : total_bytes_) : 0ull;
         return c;
     }
 
@@ -355,6 +358,7 @@ class RuntimeCore {
 
     int rank_, num_ranks_, device_;
     bool mask_on_timeout_ = false;
+    uint64_t debug_extent_override_ = 0;
     bool debug_checks_ = false;  // range-check row addresses on the device (env DEEPEP_DEBUG_CHECKS=1 or set_debug_checks)
     bool available_ = false, released_ = false;
     void* base_ = nullptr;

@@ -171,7 +171,8 @@ struct LLDispatchArgs {
     int64_t* layout_range;        // [L,R]
     int* cumulative_stats;        // [L] or nullptr
     int64_t* wait_cost_stats;     // [R] or nullptr
-    int* send_slot;               // [T,K] slot of each selection inside its (expert, me) segment; scratch kept for combine
+    int* send_row;                // [T,K] or nullptr: row of each selection inside its expert's [N, hidden] block at the expert's rank
+                                  // (-1 = not sent); the pull form of combine reads the output row back from there
     int num_sms;
 };
 cudaError_t launch_ll_dispatch(const LLDispatchArgs* a, int num_virtual, cudaStream_t stream);
@@ -185,11 +186,17 @@ struct LLCombineArgs {
     const float* topk_weights;    // [T,K]
     const int* src_info;          // [L,N]
     const int64_t* layout_range;  // [L,R]
-    __nv_bfloat16* out;           // [T,hidden]
+    __nv_bfloat16* out;           // [T,hidden] device memory or pinned host memory
     int64_t* wait_cost_stats;     // [R] or nullptr
     int num_tokens, hidden, num_topk, num_experts, num_max_tokens;
     int phases;
     int num_sms;
+    // pull form (x lives in this rank's symmetric buffer, every rank's in its own): x_off is posted to the home ranks,
+    // which read the rows in place; send_row [T,K] comes from the dispatch of the same handle
+    int pull;
+    uint64_t x_off;
+    const int* send_row;
+    int close_barrier;            // pull form: readers report back before the kernel ends (x is a caller-owned tensor)
 };
 cudaError_t launch_ll_combine(const LLCombineArgs* a, int num_virtual, cudaStream_t stream);
 

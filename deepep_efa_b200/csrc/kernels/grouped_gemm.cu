@@ -354,6 +354,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int tiles_fixed = p.mode == 1 ? ((p.n + C::kTileRows - 1) / C::kTileRows) * (p.k / kBlockN) : 0;
         for (int g = 0; g < G; ++g) {
             tile_start[g] = run;
+            // native block scaling reads one scale atom per 128-row tile, so a group that does not start on a tile boundary
+            // would be scaled with its neighbour's factors: flag it (value 2) instead of returning silently wrong numbers
+            if (kMx && (p.m_offsets[g] & 127) != 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 2);
             if (p.mode == 0) {
                 const int rows = (p.m_ends != nullptr ? p.m_ends[g] : p.m_offsets[g + 1]) - p.m_offsets[g];
                 run += ((max(rows, 0) + C::kTileRows - 1) / C::kTileRows) * tiles_n;
@@ -439,6 +442,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ================= TMA producer =================
         if (lane == 0) {
             int stage = 0, phase = 0, g = 0;
+            int issued = 0;  // stages armed so far (saturating), for the drain on the abort path
             TileInfo ti;
             bool ok = true;
             for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
@@ -457,6 +461,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         tma_load_2d_pair(&map_a, leader_full, sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
                         tma_load_2d_pair(&map_b, leader_full, sb, ti.b_k0 + kb * elem_per_kb,
                                          (kSwiGLU && cta_rank == 1) ? ti.b_row2 : ti.b_row);  // SwiGLU: gate half / up half
+                        if (issued < C::kStages) ++issued;
                         if (++stage == C::kStages) {
                             stage = 0;
                             phase ^= 1;
@@ -479,21 +484,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     } else {
                         tma_load_2d(&map_b, &full[stage], sb, ti.b_k0 + kb * elem_per_kb, ti.b_row);
                     }
+                    if (issued < C::kStages) ++issued;
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
             }
-            // Own copies in flight land in this CTA's shared memory: wait for them before the CTA may exit.
-            if (!ok && kPair && cta_rank == 1) {
-                const long long t0 = clock64();  // the peer's copies signal the leader's barriers: give them a bounded time
-                while (clock64() - t0 < 400000) {
-                }
-            } else if (!ok) {
-                for (int s = 0; s < C::kStages; ++s) {
+            // Own copies in flight land in this CTA's shared memory: before the CTA may exit, wait (bounded) for every stage
+            // that was armed but whose completion this lane has not yet seen. `stage`/`phase` point at the next stage to
+            // fill, so the kStages stages before it are the candidates, each with the phase it was armed in.
+            if (!ok) {
+                if (kPair && cta_rank == 1) {
+                    // the peer's copies signal the leader's barriers, which this CTA cannot poll: give them a fixed grace time
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && clock64() - t0 < limit) {
+                    while (clock64() - t0 < 400000) {
+                    }
+                } else {
+                    int st = stage, ph = phase;
+                    for (int i = 0; i < C::kStages && i < issued; ++i) {
+                        if (--st < 0) {
+                            st = C::kStages - 1;
+                            ph ^= 1;
+                        }
+                        const long long t0 = clock64();
+                        while (!mbar_try_wait(&full[st], ph) && clock64() - t0 < limit) {
+                        }
                     }
                 }
             }

@@ -9,9 +9,15 @@
 //     of the [L, N, hidden] output,
 //   * arrival is counted per source rank with monotonic release reductions; the last CTA derives
 //     packed_recv_count / layout_range from the counts and waits for the rows.
-// combine (one launch): expert ranks push their BF16 rows into the home rank's [E][max_tokens] stage
-// (address = (expert, token), so no metadata travels), the home rank waits per source, then one CTA
-// per token does sum_k w[t,k] * row in fp32 and writes BF16 once — deterministic order, no atomics.
+// combine (one launch), two forms chosen by where the expert outputs live:
+//   * pull (outputs in symmetric memory: the zero-copy buffer or an arena tensor): every rank posts "my outputs are
+//     final, at this offset" to all home ranks; one CTA per token then loads the token's K rows straight from the
+//     peers (their position was recorded by dispatch), does sum_k w[t,k] * row in fp32 registers and writes BF16 once.
+//     No stage buffer, no second pass, one flag hop;
+//   * push (outputs in ordinary device memory): expert ranks push their BF16 rows into the home rank's
+//     [E][max_tokens] stage (address = (expert, token), so no metadata travels), the home rank waits per source,
+//     then reduces as above.
+//   Both are deterministic (fixed k order, no atomics) and may write the result to pinned host memory.
 //
 // `phases` splits either kernel into its send (bit 0) and receive (bit 1) half for the
 // return_recv_hook contract. Sequence numbers and expected-arrival totals live on the device, so a
@@ -111,7 +117,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
 
     extern __shared__ int s_mem[];
     int* s_idx = s_mem;              // [T*K] expert id of every selection of this rank
-    int* s_hist = s_mem + T * K;     // [E] (tail CTA only)
+    int* s_hist = s_mem + T * K;     // [E] tail CTA: my counts per expert; token CTAs: selections per expert among earlier tokens
     __shared__ int s_ok;
     __shared__ int s_mask[kMaxRanks];
     __shared__ int s_row[kMaxTopk];      // destination row inside the expert, -1 = skip
@@ -164,52 +170,73 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
 
     if (do_send && !is_tail_cta) {
         const bool pow2 = a.round_scale != 0 || a.use_ue8m0 != 0;
+        // s_hist[e] = selections of expert e among the tokens before `hist_upto`; tokens are visited in rising order, so
+        // the running histogram is advanced instead of rescanning all earlier selections for every token
+        for (int i = tid; i < E; i += kLLThreads) s_hist[i] = 0;
+        int hist_upto = 0;
+        bool counts_known = false;
+        __syncthreads();
         for (int t = blockIdx.x; t < T; t += num_token_ctas) {
             // First chunk of the row is quantised while the counts of the other ranks are still in flight.
             const char* xrow = reinterpret_cast<const char*>(a.x) + (size_t)t * H * 2;
             QuantChunk qc;
             const bool act0 = tid * 16 < H;
             if (a.use_fp8) qc = quantize_chunk(xrow, tid * 16, act0, pow2, a.use_ue8m0 != 0);
+            for (int i = hist_upto * K + tid; i < t * K; i += kLLThreads)
+                if (s_idx[i] >= 0) atomicAdd(&s_hist[s_idx[i]], 1);
+            hist_upto = t;
+            __syncthreads();
             // slot of selection (t,k) among this rank's earlier selections of the same expert
-            for (int k = warp; k < K; k += kLLWarps) {
-                const int e = s_idx[t * K + k];
-                int n = 0;
-                if (e >= 0)
-                    for (int i = lane; i < t * K + k; i += 32) n += (s_idx[i] == e) ? 1 : 0;
-                n = warp_sum(n);
-                if (lane == 0) {
-                    s_row[k] = e >= 0 ? n : -1;
-                    s_dst_rank[k] = e >= 0 ? e / L : 0;
-                    s_dst_le[k] = e >= 0 ? e % L : 0;
-                    if (a.send_slot != nullptr) a.send_slot[t * K + k] = e >= 0 ? n : -1;
+            if (tid < K) {
+                const int e = s_idx[t * K + tid];
+                int n = -1;
+                if (e >= 0) {
+                    n = s_hist[e];
+                    for (int k2 = 0; k2 < tid; ++k2) n += (s_idx[t * K + k2] == e) ? 1 : 0;
                 }
+                s_row[tid] = n;
+                s_dst_rank[tid] = e >= 0 ? e / L : 0;
+                s_dst_le[tid] = e >= 0 ? e % L : 0;
             }
             // counts of the ranks before me decide where my segment starts
-            if (tid < me && !s_mask[tid]) {
+            if (!counts_known && tid < me && !s_mask[tid]) {
                 const long long t0 = clock64();
                 if (!wait_ge_sys(&my->ll_count_seq[P][tid], seq, c.timeout_cycles)) {
                     report(c.status, kTimeoutLLCount, me, tid, 0);
-                    s_ok = 0;
+                    if (c.mask_on_timeout) {
+                        // shrink mode: a silent rank sends nothing to anybody, so every sender drops its counts alike
+                        st_relaxed_sys(&my->ll_mask[tid], 1);
+                        s_mask[tid] = 1;
+                    } else {
+                        s_ok = 0;
+                    }
                 }
                 if (a.wait_cost_stats != nullptr && blockIdx.x == 0) atomicAdd((unsigned long long*)&a.wait_cost_stats[tid], (unsigned long long)(clock64() - t0));
             }
+            counts_known = true;
             __syncthreads();
-            if (!s_ok) return;
+            if (!s_ok) break;  // falls through to the completion ticket; nothing was sent by this CTA
             if (traced) trace_stamp(c, kFamLLDispatch, 0, 2);
-            if (tid < K && s_row[tid] >= 0) {
-                const int e = s_dst_rank[tid] * L + s_dst_le[tid];
-                int begin = 0;
-                for (int src = 0; src < me; ++src)
-                    if (!s_mask[src]) begin += __ldcg(&my_counts[(size_t)src * E + e]);
-                const int row = begin + s_row[tid];
-                const size_t row_bytes = (size_t)H * (a.use_fp8 ? 1 : 2);
-                if (row >= N || s_mask[s_dst_rank[tid]] ||
-                    !peer_range_ok(c, s_dst_rank[tid], c.at<char>(s_dst_rank[tid], a.region.recv_x_off[P]) + ((size_t)s_dst_le[tid] * N + (row < N ? row : 0)) * row_bytes, row_bytes, 3))
-                    s_row[tid] = -1;  // row >= N cannot happen with a consistent max_tokens
-                else {
-                    s_row[tid] = row;
-                    atomicAdd(&s_sent[s_dst_rank[tid]], 1);
+            if (tid < K) {
+                int final_row = -1;
+                if (s_row[tid] >= 0) {
+                    const int e = s_dst_rank[tid] * L + s_dst_le[tid];
+                    int begin = 0;
+                    for (int src = 0; src < me; ++src)
+                        if (!s_mask[src]) begin += __ldcg(&my_counts[(size_t)src * E + e]);
+                    const int row = begin + s_row[tid];
+                    const size_t row_bytes = (size_t)H * (a.use_fp8 ? 1 : 2);
+                    if (row >= N || s_mask[s_dst_rank[tid]] ||
+                        !peer_range_ok(c, s_dst_rank[tid], c.at<char>(s_dst_rank[tid], a.region.recv_x_off[P]) + ((size_t)s_dst_le[tid] * N + (row < N ? row : 0)) * row_bytes, row_bytes, 3)) {
+                        s_row[tid] = -1;  // row >= N cannot happen with a consistent max_tokens
+                    } else {
+                        s_row[tid] = row;
+                        final_row = row;
+                        atomicAdd(&s_sent[s_dst_rank[tid]], 1);
+                    }
                 }
+                // where this selection landed at its expert's rank: the pull form of combine reads the output row back from there
+                if (a.send_row != nullptr) a.send_row[t * K + tid] = final_row;
             }
             __syncthreads();
             if (traced) trace_stamp(c, kFamLLDispatch, 0, 3);
@@ -273,9 +300,9 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
             if (a.wait_cost_stats != nullptr) atomicAdd((unsigned long long*)&a.wait_cost_stats[tid], (unsigned long long)(clock64() - t0));
         }
         __syncthreads();
-        if (!s_ok) return;
         trace_stamp(c, kFamLLDispatch, 1, 3);
-        for (int le = tid; le < L; le += kLLThreads) {
+        const bool counts_ok = s_ok != 0;  // a failed count wait (without shrink mode) skips the layout, never the completion ticket
+        for (int le = tid; counts_ok && le < L; le += kLLThreads) {
             int run = 0;
             for (int src = 0; src < R; ++src) {
                 const int cnt = s_mask[src] ? 0 : __ldcg(&my_counts[(size_t)src * E + me * L + le]);
@@ -286,7 +313,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
             if (a.cumulative_stats != nullptr) a.cumulative_stats[le] += run;
         }
         // rows expected from every source: one warp per source sums its L counts
-        for (int src = warp; src < R; src += kLLWarps) {
+        for (int src = warp; counts_ok && src < R; src += kLLWarps) {
             int sum = 0;
             if (!s_mask[src])
                 for (int le = lane; le < L; le += 32) sum += __ldcg(&my_counts[(size_t)src * E + me * L + le]);
@@ -295,7 +322,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
         }
         __syncthreads();
         trace_stamp(c, kFamLLDispatch, 1, 4);
-        if (tid < R && !s_mask[tid]) {
+        if (counts_ok && tid < R && !s_mask[tid]) {
             uint64_t* ew = expected_word(c, 0, P, tid);
             const uint64_t want = *ew + (uint64_t)s_expected[tid];
             const long long t0 = clock64();
@@ -355,6 +382,23 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine(const __grid_constant__
     const int tslot = blockIdx.x == 0 ? 0 : 1;
     if (traced) trace_stamp(c, kFamLLCombine, tslot, 0);
     __syncthreads();
+    if (do_recv) {
+        // rows I expect from every rank = my valid selections that live there (warp-aggregated count); done first so
+        // that it does not sit between the last arriving row and the reduction
+        for (int i0 = 0; i0 < T * K; i0 += kLLThreads) {
+            const int i = i0 + tid;
+            int rk = -1;
+            if (i < T * K) {
+                const int64_t e = a.topk_idx[i];
+                if (e >= 0 && e < E) rk = (int)e / L;
+            }
+            for (int r = 0; r < R; ++r) {
+                const unsigned b = __ballot_sync(0xffffffffu, rk == r);
+                if (lane == 0 && b) atomicAdd(&s_expected[r], __popc(b));
+            }
+        }
+        __syncthreads();
+    }
 
     if (do_send) {
         // ---- enumerate the valid rows compactly: row r -> (local expert, slot) through a prefix over experts ----
@@ -428,20 +472,6 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine(const __grid_constant__
     }
 
     if (do_recv) {
-        // rows I expect from every rank = my valid selections that live there (warp-aggregated count)
-        for (int i0 = 0; i0 < T * K; i0 += kLLThreads) {
-            const int i = i0 + tid;
-            int rk = -1;
-            if (i < T * K) {
-                const int64_t e = a.topk_idx[i];
-                if (e >= 0 && e < E) rk = (int)e / L;
-            }
-            for (int r = 0; r < R; ++r) {
-                const unsigned b = __ballot_sync(0xffffffffu, rk == r);
-                if (lane == 0 && b) atomicAdd(&s_expected[r], __popc(b));
-            }
-        }
-        __syncthreads();
         if (traced) trace_stamp(c, kFamLLCombine, tslot, 3);
         if (tid < R && !s_mask[tid]) {
             const uint64_t want = *expected_word(c, 1, P, tid) + (uint64_t)s_expected[tid];
@@ -526,9 +556,142 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine(const __grid_constant__
     }
 }
 
+// Pull form: the expert outputs of every rank sit in its symmetric buffer, so the home rank reads the K rows of a token
+// where dispatch put them (send_row) and reduces them in registers. The only signalling is one mailbox word per
+// (expert rank, home rank): "outputs final, at this offset".
+template <int V>
+__global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_constant__ ArgPack<LLCombineArgs, V> pack) {
+    pdl_wait_predecessor();
+    pdl_release_successor();
+    const LLCombineArgs& a = pack.a[blockIdx.y];
+    const RankCtx& c = a.ctx;
+    const int R = c.num_ranks, me = c.rank, T = a.num_tokens, K = a.num_topk, E = a.num_experts;
+    const int L = E / R, H = a.hidden;
+    const int N = R * a.num_max_tokens;
+    const int n16 = H / 8;
+    const int tid = threadIdx.x;
+    const uint64_t seq = next_seq(c, kFamLLCombine);
+    const bool do_send = a.phases & 1, do_recv = a.phases & 2;
+    ControlBlock* my = c.my_ctrl();
+    __shared__ int s_mask[kMaxRanks];
+    __shared__ const int4* s_base[kMaxRanks];
+    __shared__ int s_ok;
+    __shared__ long long s_sel_row[kMaxTopk];  // element offset (in int4) of selection k inside its rank's x, -1 = skip
+    __shared__ int s_sel_rank[kMaxTopk];
+    __shared__ float s_sel_w[kMaxTopk];
+    if (tid < kMaxRanks) s_mask[tid] = tid < R ? __ldcg(&my->ll_mask[tid]) : 1;
+    if (tid == 0) s_ok = 1;
+    const bool traced = blockIdx.x == 0 || blockIdx.x == gridDim.x - 1;
+    const int tslot = blockIdx.x == 0 ? 0 : 1;
+    if (traced) trace_stamp(c, kFamLLCombine, tslot, 0);
+    __syncthreads();
+
+    if (do_send && blockIdx.x == 0 && tid < R && !s_mask[tid]) {
+        // the kernel that produced x is complete (stream order), so its writes are in this GPU's memory system
+        const uint64_t w[1] = {a.x_off};
+        mailbox_post(c, kMbLLCombine, tid, w, 1, seq);
+    }
+    if (traced) trace_stamp(c, kFamLLCombine, tslot, 1);
+
+    if (do_recv) {
+        if (tid < R && !s_mask[tid]) {
+            uint64_t w[1];
+            const long long t0 = clock64();
+            if (!mailbox_wait(c, kMbLLCombine, tid, seq, w, 1)) {
+                report(c.status, kTimeoutCombineReady, me, tid, 1);
+                if (c.mask_on_timeout) {
+                    st_relaxed_sys(&my->ll_mask[tid], 1);
+                    s_mask[tid] = 1;
+                } else {
+                    s_ok = 0;
+                }
+            } else {
+                s_base[tid] = c.at<const int4>(tid, w[0]);
+            }
+            if (a.wait_cost_stats != nullptr && blockIdx.x == 0) atomicAdd((unsigned long long*)&a.wait_cost_stats[tid], (unsigned long long)(clock64() - t0));
+        }
+        __syncthreads();
+        if (traced) trace_stamp(c, kFamLLCombine, tslot, 4);
+        if (s_ok) {
+            for (int t = blockIdx.x; t < T; t += gridDim.x) {
+                __syncthreads();
+                if (tid < K) {
+                    const int64_t e = a.topk_idx[(size_t)t * K + tid];
+                    const int row = a.send_row[(size_t)t * K + tid];
+                    bool ok = e >= 0 && e < E && row >= 0 && row < N && !s_mask[(int)e / L];
+                    const int r = ok ? (int)e / L : 0;
+                    const long long off = ok ? ((long long)((int)e % L) * N + row) * n16 : -1;
+                    if (ok && !peer_range_ok(c, r, s_base[r] + off, (size_t)n16 * 16, 5)) ok = false;
+                    s_sel_row[tid] = ok ? off : -1;
+                    s_sel_rank[tid] = r;
+                    s_sel_w[tid] = ok ? a.topk_weights[(size_t)t * K + tid] : 0.f;
+                }
+                __syncthreads();
+                // two 16-byte columns per thread per pass, all loads of a pass in flight together
+                for (int i0 = 0; i0 < n16; i0 += 2 * kLLThreads) {
+                    const int ia = i0 + tid, ib = i0 + kLLThreads + tid;
+                    float acc[2][8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[0][j] = acc[1][j] = 0.f;
+                    for (int k0 = 0; k0 < K; k0 += 8) {
+                        int4 va[8], vb[8];
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) {
+                            const int k = k0 + kk;
+                            const long long row = k < K ? s_sel_row[k] : -1;
+                            const int4* base = row >= 0 ? s_base[s_sel_rank[k]] + row : nullptr;
+                            va[kk] = (row >= 0 && ia < n16) ? ld_peer(base + ia) : make_int4(0, 0, 0, 0);
+                            vb[kk] = (row >= 0 && ib < n16) ? ld_peer(base + ib) : make_int4(0, 0, 0, 0);
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) {
+                            const int k = k0 + kk;
+                            const float w = k < K ? s_sel_w[k] : 0.f;
+                            const uint32_t ua[4] = {(uint32_t)va[kk].x, (uint32_t)va[kk].y, (uint32_t)va[kk].z, (uint32_t)va[kk].w};
+                            const uint32_t ub[4] = {(uint32_t)vb[kk].x, (uint32_t)vb[kk].y, (uint32_t)vb[kk].z, (uint32_t)vb[kk].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 pa = bf16x2_to_f2(ua[j]), pb = bf16x2_to_f2(ub[j]);
+                                acc[0][2 * j] = fmaf(w, pa.x, acc[0][2 * j]);
+                                acc[0][2 * j + 1] = fmaf(w, pa.y, acc[0][2 * j + 1]);
+                                acc[1][2 * j] = fmaf(w, pb.x, acc[1][2 * j]);
+                                acc[1][2 * j + 1] = fmaf(w, pb.y, acc[1][2 * j + 1]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int i = h == 0 ? ia : ib;
+                        if (i >= n16) continue;
+                        int4 o;
+                        o.x = (int)f2_to_bf16x2(acc[h][0], acc[h][1]);
+                        o.y = (int)f2_to_bf16x2(acc[h][2], acc[h][3]);
+                        o.z = (int)f2_to_bf16x2(acc[h][4], acc[h][5]);
+                        o.w = (int)f2_to_bf16x2(acc[h][6], acc[h][7]);
+                        st_stream(reinterpret_cast<int4*>(a.out) + (size_t)t * n16 + i, o);
+                    }
+                }
+            }
+        }
+        if (traced) trace_stamp(c, kFamLLCombine, tslot, 5);
+        // Readers of a caller-owned symmetric tensor tell its owner when they are done (the zero-copy buffer needs no such
+        // hop: a rank reuses it only two dispatches later, by which time every reader has been seen to finish).
+        const bool last = cta_is_last(c.local_scratch + kTicketLLCombine, gridDim.x);
+        if (last) {
+            if (a.close_barrier && tid < R && !s_mask[tid]) st_release_sys(&c.ctrl(tid)->barrier_in[kBarLL][me], seq);
+            if (tid == 0) commit_seq(c, kFamLLCombine, seq);
+        }
+        if (a.close_barrier && blockIdx.x == 0 && tid < R && !s_mask[tid]) {
+            if (!wait_ge_sys(&my->barrier_in[kBarLL][tid], seq, c.timeout_cycles)) report(c.status, kTimeoutBarrier, me, tid, 300);
+        }
+        if (traced) trace_stamp(c, kFamLLCombine, tslot, 6);
+    }
+}
+
 }  // namespace ll
 
 cudaError_t launch_ll_combine(const LLCombineArgs* a, int nv, cudaStream_t stream) {
+    if (a[0].pull) return DX_LAUNCH_RANKED_PDL(ll::combine_pull, LLCombineArgs, a, nv, a[0].num_sms, kLLThreads, 0, stream);
     const size_t smem = ((size_t)a[0].num_experts / a[0].ctx.num_ranks + 1) * sizeof(int);
     return DX_LAUNCH_RANKED_PDL(ll::combine, LLCombineArgs, a, nv, a[0].num_sms, kLLThreads, smem, stream);
 }

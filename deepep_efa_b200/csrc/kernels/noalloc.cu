@@ -62,8 +62,18 @@ extern "C" int dx_get_dispatch_layout_noalloc(const int64_t* topk_idx, int num_t
         return fail(DX_NOALLOC_TOO_LARGE,
                     "problem needs %lld scratch ints but the built-in scratch holds %lld; use the allocating get_dispatch_layout",
                     (long long)need, (long long)DX_NOALLOC_MAX_SCRATCH_INTS);
-    if ((size_t)(num_experts + num_ranks) * sizeof(int) > 48 * 1024)
-        return fail(DX_NOALLOC_TOO_LARGE, "num_experts + num_ranks = %lld does not fit the kernel's shared-memory histogram", num_experts + num_ranks);
+    // same bound as the launcher's shared-memory request (experts + 2 * ranks bins), checked before anything is queued
+    if ((size_t)(num_experts + 2 * num_ranks) * sizeof(int) > 48 * 1024)
+        return fail(DX_NOALLOC_TOO_LARGE, "num_experts + 2 * num_ranks = %lld bins do not fit the kernel's shared-memory histogram",
+                    num_experts + 2 * num_ranks);
+    // With 8 ranks the kernel writes one token's eight membership bytes as a single 8-byte store; a bool* is only
+    // guaranteed 1-byte alignment (a slice of a larger buffer), so an unaligned output is refused here instead of
+    // faulting on the device.
+    if (num_ranks == 8 && (reinterpret_cast<uintptr_t>(is_token_in_rank) & 7u) != 0)
+        return fail(DX_NOALLOC_BAD_ARGUMENT, "with 8 ranks is_token_in_rank must be 8-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(topk_idx) & 7u) != 0 || (reinterpret_cast<uintptr_t>(num_tokens_per_rank) & 3u) != 0 ||
+        (reinterpret_cast<uintptr_t>(num_tokens_per_expert) & 3u) != 0)
+        return fail(DX_NOALLOC_BAD_ARGUMENT, "topk_idx must be 8-byte aligned and the count outputs 4-byte aligned");
     int code = DX_NOALLOC_OK;
     int* scratch = scratch_for_current_device(&code);
     if (scratch == nullptr) return code;

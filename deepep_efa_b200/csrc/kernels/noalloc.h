@@ -18,6 +18,10 @@
 //    Make that first call before starting any stream capture.
 //  * All calls on a device share the one array. Two calls whose kernels overlap on the GPU (different
 //    streams, no dependency) race on it; serialise them on one stream or with events.
+//  * `stream` must belong to the device that is current when the call is made (the scratch address is the current
+//    device's copy of the array).
+//  * With num_ranks == 8 `is_token_in_rank` must be 8-byte aligned (each token's row is written with one store);
+//    an unaligned pointer is refused with DX_NOALLOC_BAD_ARGUMENT and nothing is launched.
 //  * Nothing is allocated or freed: no cudaMalloc/cudaFree, no PyTorch tensors.
 #pragma once
 

@@ -244,6 +244,7 @@ enum BarrierKind : int { kBarExplicit = 0, kBarDispatch = 1, kBarCombine = 2, kB
 
 __device__ __forceinline__ bool cta_rank_barrier(const RankCtx& c, uint64_t seq) {
     __shared__ int s_ok;
+    __syncthreads();  // readers of an earlier call's result are done before the flag is rewritten
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < c.num_ranks) {

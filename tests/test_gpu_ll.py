@@ -119,3 +119,55 @@ def test_ll_masked_rank_is_skipped():
         assert st.tolist() == [0, 0, 0, 0]
     finally:
         vc.destroy()
+
+
+@pytest.mark.parametrize("R,T,H,E,K,num_sms", [(2, 300, 512, 16, 8, 9), (4, 40, 1024, 32, 6, None), (1, 128, 7168, 16, 8, 24)])
+def test_ll_pull_equals_push_host_out_and_sm_knob(R, T, H, E, K, num_sms):
+    """The pull form of combine (expert outputs in symmetric memory: zero-copy buffer or arena tensor) gives bit-identical
+    results to the staged push form; the result may land in pinned host memory; a bounded grid (several tokens per CTA,
+    which exercises the running per-expert slot count of dispatch) changes nothing."""
+    from deepep_efa_b200 import Buffer
+    from deepep_efa_b200.parallel.virtual import VirtualCluster
+    from deepep_efa_b200.reference import oracle
+    vc = VirtualCluster(R, num_nvl_bytes=(2 << 20) + 2 * (E // R) * R * T * H * 2,
+                        num_rdma_bytes=Buffer.get_low_latency_rdma_size_hint(T, H, R, E), timeout_ms=2000)
+    Buffer.set_low_latency_num_sms(num_sms)
+    try:
+        L = E // R
+        xs, idxs, ws = [], [], []
+        for r in range(R):
+            i, w = make_routing(T, E, K, "cuda", seed=70 + r, masked_fraction=0.1)
+            idxs.append(i), ws.append(w), xs.append(make_tokens(T, H, "cuda", seed=40 + r))
+        res = vc.low_latency_dispatch(xs, idxs, T, E, use_fp8=False)
+        torch.cuda.synchronize()
+        ref = oracle.low_latency_dispatch([x.cpu() for x in xs], [i.cpu() for i in idxs], T, E, False)
+        for r in range(R):
+            assert torch.equal(res[r][1].cpu(), ref[r]["packed_recv_count"])
+            for le in range(L):
+                n = int(res[r][1][le])
+                assert torch.equal(res[r][2][0][le, :n].cpu(), ref[r]["src_info"][le, :n])
+                assert torch.equal(res[r][0][le, :n].cpu(), ref[r]["packed_recv_x"][le, :n])
+        handles = [r_[2] for r_ in res]
+        ys = [(r_[0].float() * 0.5).to(torch.bfloat16) for r_ in res]            # ordinary device tensors -> push
+        push = [o[0].clone() for o in vc.low_latency_combine(ys, idxs, ws, handles)]
+        sym = []
+        for r in range(R):                                                       # arena tensors -> pull + closing barrier
+            t = vc.buffers[r].empty_symmetric(list(ys[r].shape), torch.bfloat16)
+            t.copy_(ys[r])
+            sym.append(t)
+        pull = [o[0].clone() for o in vc.low_latency_combine(sym, idxs, ws, handles)]
+        for r in range(R):                                                       # zero-copy buffer -> pull, result to host
+            vc.buffers[r].get_next_low_latency_combine_buffer(handles[r]).copy_(ys[r])
+        host = [torch.zeros(T, H, dtype=torch.bfloat16).pin_memory() for _ in range(R)]
+        vc.low_latency_combine(ys, idxs, ws, handles, zero_copy=True, outs=host)
+        torch.cuda.synchronize()
+        for b in vc.buffers:
+            b.check_status()
+        for r in range(R):
+            want = xs[r].float() * 0.5 * ws[r].masked_fill(idxs[r] == -1, 0).sum(dim=1, keepdim=True)
+            assert oracle.calc_diff(want, push[r].float()) < 2e-5
+            assert torch.equal(push[r], pull[r])
+            assert torch.equal(push[r].cpu(), host[r])
+    finally:
+        Buffer.set_low_latency_num_sms(None)
+        vc.destroy()

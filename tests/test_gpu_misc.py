@@ -64,8 +64,11 @@ def test_debug_range_check_turns_a_bad_row_into_a_status():
                                                 num_tokens_per_expert=per_expert, topk_idx=idx, topk_weights=w)
         b.check_status(sync=True)  # the checks do not fire on a healthy call
         assert torch.equal(recv_x, x)
+        # The checked extent is made smaller than the real allocation and the bad row lies between the two: if the check
+        # ever regressed, the stray store would land in this rank's own (free) arena memory instead of somewhere wild.
+        b.runtime.set_debug_extent(4 << 20)
         bad_head = handle[5].clone()
-        bad_head[5, 0] = 1 << 27  # row 2^27 of a 1 KiB row: a terabyte past the buffer
+        bad_head[5, 0] = 8192  # 8 MiB past recv_x with 1 KiB rows: outside the 4 MiB extent, inside the 32 MiB buffer
         bad = handle[:5] + (bad_head,)
         rx2, *_ = b.dispatch(x, handle=bad)
         with pytest.raises(EPTimeoutError) as ei:
@@ -74,6 +77,7 @@ def test_debug_range_check_turns_a_bad_row_into_a_status():
         keep = torch.arange(T, device="cuda") != 5
         assert torch.equal(rx2[keep], x[keep])
         b.recover()
+        b.runtime.set_debug_extent(0)
         rx3, *_ = b.dispatch(x, handle=handle)
         b.check_status(sync=True)
         assert torch.equal(rx3, x)

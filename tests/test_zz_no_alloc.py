@@ -77,4 +77,10 @@ def test_noalloc_rejects_oversized_and_bad_arguments():
     assert rc == -1
     rc = fn(None, 16, 8, 256, 8, p, p, p, stream)
     assert rc == -1
+    # 8 ranks: a membership output that is not 8-byte aligned is refused on the host, nothing is launched
+    rc = fn(p, 2, 8, 256, 8, p, p, p + 1, stream)
+    assert rc == -1 and b"aligned" in lib.dx_noalloc_last_error()
+    # the shared-memory bound is the launcher's (experts + 2 * ranks bins): 12280 + 16 bins exceed 48 KiB
+    rc = fn(p, 16, 8, 12280, 8, p, p, p, stream)
+    assert rc == -2 and b"shared-memory" in lib.dx_noalloc_last_error()
     torch.cuda.synchronize()

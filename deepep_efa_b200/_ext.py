@@ -36,11 +36,13 @@ CUDA_SOURCES = [
     "kernels/hier.cu",
     "kernels/train_ops.cu",
     "kernels/sf_atoms.cu",
+    "kernels/fused.cu",
 ]
 CPP_SOURCES = [
     "host/bindings.cpp",
     "host/gemm_bindings.cpp",
     "host/hier_bindings.cpp",
+    "host/fused_bindings.cpp",
 ]
 
 CUDA_FLAGS = [

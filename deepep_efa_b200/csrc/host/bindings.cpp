@@ -106,6 +106,13 @@ struct Runtime {
     }
 };
 
+}  // namespace
+
+// used by fused_bindings.cpp, which cannot name the module-local Runtime class
+dxh::RuntimeCore* dx_core_of(py::handle runtime) { return runtime.cast<Runtime*>()->core.get(); }
+
+namespace {
+
 cudaStream_t cur_stream(const Runtime* rt) { return c10::cuda::getCurrentCUDAStream(rt->core->device()).stream(); }
 
 void set_local_peers(std::vector<Runtime*> rts) {
@@ -372,22 +379,36 @@ void timeout_probe(Runtime* rt) {
 // ---------------------------------------------------------------------------------------------
 std::tuple<torch::Tensor, torch::Tensor> per_token_cast_to_fp8(const torch::Tensor& x, bool round_scale, bool use_ue8m0,
                                                                c10::optional<torch::Tensor> group_counts, int rows_per_group,
-                                                               c10::optional<torch::Tensor> out_q, c10::optional<torch::Tensor> out_s) {
+                                                               c10::optional<torch::Tensor> out_q, c10::optional<torch::Tensor> out_s,
+                                                               c10::optional<torch::Tensor> num_rows_dev, bool atoms) {
     DX_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "x must be contiguous bf16 [M,hidden] on the GPU");
     const int M = (int)x.size(0), H = (int)x.size(1);
     DX_CHECK(H % 128 == 0 && (!use_ue8m0 || H % 512 == 0), "hidden must be a multiple of 128 (512 for UE8M0 scales)");
     c10::cuda::CUDAGuard guard(x.device());
     auto out = out_q.has_value() ? *out_q : torch::empty({M, H}, x.options().dtype(torch::kFloat8_e4m3fn));
+    // atoms: the scales leave as the UE8M0 scale atoms of the natively block-scaled GEMM, uint8 [ceil(M/128), hidden/128, 512]
+    DX_CHECK(!atoms || !use_ue8m0, "atoms and use_ue8m0 are two different scale formats");
     torch::Tensor scales = out_s.has_value() ? *out_s
+                           : atoms ? torch::empty({(M + 127) / 128, H / 128, 512}, x.options().dtype(torch::kUInt8))
                            : (use_ue8m0 ? torch::empty({M, H / 512}, x.options().dtype(torch::kInt32))
                                         : torch::empty({M, H / 128}, x.options().dtype(torch::kFloat32)));
+    DX_CHECK(out.is_cuda() && scales.is_cuda() && out.device() == x.device() && scales.device() == x.device(), "outputs must live on x's GPU");
     DX_CHECK(out.is_contiguous() && out.numel() == (int64_t)M * H && out.element_size() == 1, "out_q must be a contiguous 1-byte [M,hidden] tensor");
-    DX_CHECK(scales.is_contiguous() && scales.numel() == (int64_t)M * (use_ue8m0 ? H / 512 : H / 128) && scales.element_size() == 4, "out_s has the wrong shape");
-    dx::Fp8CastArgs a;
+    if (atoms)
+        DX_CHECK(scales.is_contiguous() && scales.element_size() == 1 && scales.numel() >= (int64_t)((M + 127) / 128) * (H / 128) * 512, "out_s must be uint8 [ceil(M/128), hidden/128, 512]");
+    else
+        DX_CHECK(scales.is_contiguous() && scales.numel() == (int64_t)M * (use_ue8m0 ? H / 512 : H / 128) && scales.element_size() == 4, "out_s has the wrong shape");
+    dx::Fp8CastArgs a{};
     a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
     a.out = reinterpret_cast<uint8_t*>(out.data_ptr());
-    a.scales = use_ue8m0 ? nullptr : scales.data_ptr<float>();
+    a.scales = (use_ue8m0 || atoms) ? nullptr : scales.data_ptr<float>();
     a.scales_ue8m0 = use_ue8m0 ? scales.data_ptr<int32_t>() : nullptr;
+    a.sf_atoms = atoms ? scales.data_ptr<uint8_t>() : nullptr;
+    if (num_rows_dev.has_value()) {
+        DX_CHECK(num_rows_dev->is_cuda() && num_rows_dev->device() == x.device() && num_rows_dev->scalar_type() == torch::kInt32 && num_rows_dev->numel() >= 1,
+                 "num_rows_dev must be an int32 tensor on x's GPU");
+        a.num_rows_dev = num_rows_dev->data_ptr<int>();
+    }
     a.num_rows = M;
     a.hidden = H;
     a.round_scale = round_scale ? 1 : 0;
@@ -569,6 +590,7 @@ py::dict ll_layout(Runtime* rt, int num_max_tokens, int hidden, int num_experts)
 
 void bind_gemm(py::module_& m);  // gemm_bindings.cpp
 void bind_hier(py::module_& m);  // hier_bindings.cpp
+void bind_fused(py::module_& m); // fused_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "deepep_efa_b200 native runtime (sm_100a)";
@@ -655,11 +677,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("barrier", &barrier);
     m.def("timeout_probe", &timeout_probe);
     m.def("per_token_cast_to_fp8", &per_token_cast_to_fp8, py::arg("x"), py::arg("round_scale") = false, py::arg("use_ue8m0") = false,
-          py::arg("group_counts") = py::none(), py::arg("rows_per_group") = 1, py::arg("out_q") = py::none(), py::arg("out_s") = py::none());
+          py::arg("group_counts") = py::none(), py::arg("rows_per_group") = 1, py::arg("out_q") = py::none(), py::arg("out_s") = py::none(),
+          py::arg("num_rows_dev") = py::none(), py::arg("atoms") = false);
     m.def("ll_dispatch", &ll_dispatch);
     m.def("ll_combine", &ll_combine, py::arg("runtimes"), py::arg("per_rank"), py::arg("num_max_tokens"), py::arg("num_experts"),
           py::arg("parity"), py::arg("phases"), py::arg("num_sms"), py::arg("pull") = false, py::arg("close_barrier") = false);
     m.def("ll_layout", &ll_layout);
     bind_gemm(m);
     bind_hier(m);
+    bind_fused(m);
 }

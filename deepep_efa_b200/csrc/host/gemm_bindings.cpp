@@ -60,7 +60,10 @@ int clock_khz(int device) {
 torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& m_offsets, int mode, bool swiglu,
                            c10::optional<torch::Tensor> a_scales, c10::optional<torch::Tensor> b_scales,
                            c10::optional<torch::Tensor> out, int num_sms, double timeout_ms, c10::optional<torch::Tensor> m_ends,
-                           c10::optional<torch::Tensor> sfa_atoms, c10::optional<torch::Tensor> sfb_atoms) {
+                           c10::optional<torch::Tensor> sfa_atoms, c10::optional<torch::Tensor> sfb_atoms,
+                           c10::optional<torch::Tensor> ready, c10::optional<torch::Tensor> expected,
+                           c10::optional<torch::Tensor> row_info, c10::optional<torch::Tensor> scatter_bases,
+                           c10::optional<torch::Tensor> trace) {
     DXG_CHECK(a.is_cuda() && b.is_cuda() && m_offsets.is_cuda(), "operands must be CUDA tensors");
     DXG_CHECK(a.is_contiguous() && b.is_contiguous() && m_offsets.is_contiguous(), "operands must be contiguous");
     DXG_CHECK(m_offsets.scalar_type() == torch::kInt32 && m_offsets.dim() == 1 && m_offsets.numel() >= 2, "m_offsets must be int32 [G+1]");
@@ -75,8 +78,9 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     // must be refused here, it would be an illegal address there
     auto same_dev = [&](const c10::optional<torch::Tensor>& t) { return !t.has_value() || (t->is_cuda() && t->device() == a.device()); };
     DXG_CHECK(b.device() == a.device() && m_offsets.device() == a.device(), "A, B and m_offsets must live on the same GPU");
-    DXG_CHECK(same_dev(a_scales) && same_dev(b_scales) && same_dev(out) && same_dev(m_ends) && same_dev(sfa_atoms) && same_dev(sfb_atoms),
-              "scales, atoms, m_ends and out must be CUDA tensors on A's device");
+    DXG_CHECK(same_dev(a_scales) && same_dev(b_scales) && same_dev(out) && same_dev(m_ends) && same_dev(sfa_atoms) && same_dev(sfb_atoms) &&
+                  same_dev(ready) && same_dev(expected) && same_dev(row_info) && same_dev(scatter_bases) && same_dev(trace),
+              "scales, atoms, m_ends, gating / scatter tensors and out must be CUDA tensors on A's device");
     c10::cuda::CUDAGuard guard(device);
     dx::GroupedGemmArgs p{};
     p.num_groups = G;
@@ -92,8 +96,9 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         DXG_CHECK(b.size(-1) == K, "B's last dimension must equal K");
         DXG_CHECK(!swiglu || N % 2 == 0, "swiglu needs an even N (gate and up stacked)");
         const int64_t out_cols = swiglu ? N / 2 : N;
-        c = out.has_value() ? *out : torch::empty({M, out_cols}, bf16);
-        DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && c.numel() == M * out_cols, "out must be contiguous bf16 [M, N]");
+        // with the scatter epilogue nothing is stored to `c`: every row goes to the address its row_info word names
+        c = out.has_value() ? *out : torch::empty({row_info.has_value() ? (int64_t)0 : M, out_cols}, bf16);
+        DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && (row_info.has_value() || c.numel() == M * out_cols), "out must be contiguous bf16 [M, N]");
         p.m_total = (int)M;
         p.n = (int)N;
         p.k = (int)K;
@@ -104,7 +109,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
             DXG_CHECK(!swiglu || (N / 2) % 128 == 0, "native block scaling with swiglu needs N/2 % 128 == 0");
             const int64_t atoms_n = N / 128;  // plain: one atom per 128-row tile; swiglu: two atoms per 256-row tile
             DXG_CHECK(sfa_atoms->is_cuda() && sfa_atoms->scalar_type() == torch::kUInt8 && sfa_atoms->is_contiguous() &&
-                          sfa_atoms->numel() == ((M + 127) / 128) * (K / 128) * 512, "sfa_atoms must be uint8 [ceil(M/128), K/128, 512]");
+                          sfa_atoms->numel() >= ((M + 127) / 128) * (K / 128) * 512, "sfa_atoms must be uint8 [ceil(M/128), K/128, 512]");
             DXG_CHECK(sfb_atoms->is_cuda() && sfb_atoms->scalar_type() == torch::kUInt8 && sfb_atoms->is_contiguous() &&
                           sfb_atoms->numel() == (int64_t)G * atoms_n * (K / 128) * 512, "sfb_atoms must be uint8 [G, N/128 atoms, K/128, 512]");
             p.mx_wide = (swiglu && sfb_atoms->size(-1) == 1024) ? 1 : 0;  // the atom layout says which tile width it was built for
@@ -146,6 +151,25 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         if (pr != nullptr && (pr[0] == '0' || pr[0] == '1')) p.cta_pairs = pr[0] == '1';
         else p.cta_pairs = (!fp8 && p.m_ends == nullptr && (mode == 1 || (int64_t)p.m_total >= 1024 * (int64_t)G)) ? 1 : 0;
         if (p.num_sms < 2) p.cta_pairs = 0;
+    }
+    if (ready.has_value() || expected.has_value()) {
+        DXG_CHECK(mode == 0 && ready.has_value() && expected.has_value(), "ready and expected go together (M-grouped mode)");
+        DXG_CHECK(ready->element_size() == 8 && expected->element_size() == 8 && ready->is_contiguous() && expected->is_contiguous() &&
+                      ready->numel() >= G && expected->numel() >= G, "ready / expected must be 64-bit [G]");
+        p.ready = reinterpret_cast<const unsigned long long*>(ready->data_ptr());
+        p.expected = reinterpret_cast<const unsigned long long*>(expected->data_ptr());
+    }
+    if (row_info.has_value() || scatter_bases.has_value()) {
+        DXG_CHECK(mode == 0 && !swiglu && row_info.has_value() && scatter_bases.has_value() && m_ends.has_value(),
+                  "the scatter epilogue needs row_info, scatter_bases and m_ends (M-grouped mode, no swiglu)");
+        DXG_CHECK(row_info->scalar_type() == torch::kInt32 && row_info->is_contiguous() && row_info->numel() >= p.m_total, "row_info must be int32 [M]");
+        DXG_CHECK(scatter_bases->element_size() == 8 && scatter_bases->is_contiguous() && scatter_bases->numel() >= 1, "scatter_bases must be 64-bit pointers");
+        p.row_info = row_info->data_ptr<int>();
+        p.scatter_bases = reinterpret_cast<const unsigned long long*>(scatter_bases->data_ptr());
+    }
+    if (trace.has_value()) {
+        DXG_CHECK(trace->element_size() == 8 && trace->is_contiguous() && trace->numel() >= 2, "trace must be 64-bit [2]");
+        p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
     }
     p.error_flag = error_flag(device).data_ptr<int>();
     p.timeout_cycles = (long long)(timeout_ms * (double)clock_khz(device));
@@ -302,7 +326,9 @@ void bind_gemm(py::module_& m) {
     m.def("rowdot", &rowdot);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("m_offsets"), py::arg("mode") = 0, py::arg("swiglu") = false,
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
-          py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none(), py::arg("sfa_atoms") = py::none(), py::arg("sfb_atoms") = py::none());
+          py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none(), py::arg("sfa_atoms") = py::none(), py::arg("sfb_atoms") = py::none(),
+          py::arg("ready") = py::none(), py::arg("expected") = py::none(), py::arg("row_info") = py::none(),
+          py::arg("scatter_bases") = py::none(), py::arg("trace") = py::none());
     m.def("build_plan", &build_plan);
     m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
     m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());

@@ -54,6 +54,7 @@ inline const char* status_name(int code) {
         case dx::kTimeoutGemm: return "timeout inside grouped GEMM pipeline";
         case dx::kBadArgument: return "kernel rejected its arguments";
         case dx::kTimeoutTest: return "timeout probe (expected in tests)";
+        case dx::kTimeoutFusedNotify: return "timeout waiting for expert counts (expert-major dispatch)";
         case dx::kBadPeerAccess: return "debug bounds check: a row address fell outside the peer's symmetric buffer (access skipped)";
         default: return "unknown status";
     }
@@ -67,7 +68,8 @@ struct HostWords {
 };
 
 constexpr int kLocalScratchInts = 64;
-constexpr int kLocalSeqWords = dx::kNumFamilies + 2 * 2 * dx::kMaxRanks;  // sequences + expected arrivals
+// sequences + low-latency expected arrivals + expected rows per local expert of the expert-major dispatch
+constexpr int kLocalSeqWords = dx::kFusedExpectedWord0 + dx::kMaxLocalExperts;
 
 class RuntimeCore {
   public:
@@ -325,6 +327,7 @@ class RuntimeCore {
     uint64_t ll_bytes() const { return ll_bytes_; }
     const Arena& arena() const { return arena_; }
     uint64_t* never_set_flag() const { return never_set_flag_; }
+    uint64_t* local_seq() const { return local_seq_; }
     dx::ControlBlock* control() const { return reinterpret_cast<dx::ControlBlock*>(base_); }
 
   private:

@@ -132,6 +132,48 @@ struct SegmentedCopyArgs {
 };
 cudaError_t launch_segmented_copy(const SegmentedCopyArgs& a, cudaStream_t stream);
 
+// ---- expert-major dispatch of the fused MoE layer (fused.cu) -----------------------------------
+struct EmNotifyArgs {
+    RankCtx ctx;
+    const int64_t* topk_idx;      // [T,K] global expert ids, -1 = unselected
+    int num_tokens, num_topk, num_experts;
+    int unit_rows;                // rows per work unit of the dispatch kernel
+    int rows_cap;                 // rows every rank's receive buffers hold (the same on all ranks)
+    // where MY received rows, their scales, their (source rank, selection) words and my combine stage live (offsets inside
+    // my symmetric buffer); published to all peers with the counts
+    uint64_t recv_x_off, recv_scales_off, recv_info_off, stage_off;
+    // outputs, rank-local device memory
+    int* my_counts;               // [E] my selections per expert
+    int* sel_list;                // [E, T] selection ids (t*K + k) of every expert in token order
+    int* send_base;               // [E] row of my first selection of expert e inside e's rank
+    int* unit_start;              // [E+1] exclusive prefix of work units in send order (local expert major, rank minor)
+    int* m_offsets;               // [L+1] 128-aligned first row of my local experts; [L] = rows in use
+    int* m_ends;                  // [L] end of the valid rows of every local expert
+    uint64_t* peer_bases;         // [4, R] device pointers of every rank's rows / scales / info / stage
+};
+cudaError_t launch_em_notify(const EmNotifyArgs* a, int num_virtual, cudaStream_t stream);
+
+struct EmDispatchArgs {
+    RankCtx ctx;
+    const __nv_bfloat16* x;       // [T, hidden]
+    int num_tokens, hidden, num_topk, num_experts;
+    int unit_rows, round_scale;
+    int native_atoms;             // 1: scales are written as the UE8M0 words of [row tile][K block][512] scale atoms
+    const int* my_counts;
+    const int* sel_list;
+    const int* send_base;
+    const int* unit_start;
+    const uint64_t* peer_bases;
+    int* dst_row;                 // [T*K] or nullptr: row each selection was stored to (entries of unselected slots untouched)
+    int num_sms;
+    unsigned long long* trace;    // optional [2]: earliest start / latest end of the kernel (global timer, ns)
+};
+cudaError_t launch_em_dispatch(const EmDispatchArgs* a, int num_virtual, cudaStream_t stream);
+
+// out[t] = sum_k w[t,k] * stage[t*K + k] over the selections with a valid expert id (bf16 rows, fp32 accumulation)
+cudaError_t launch_stage_reduce(const void* stage, void* out, const int64_t* topk_idx, const float* w, int num_tokens, int num_topk,
+                                int num_experts, int hidden, cudaStream_t stream);
+
 // ---- standalone FP8 cast ------------------------------------------------------------------
 struct Fp8CastArgs {
     const __nv_bfloat16* x;   // [M,hidden]
@@ -143,6 +185,8 @@ struct Fp8CastArgs {
     // optional masking for grouped layouts: row r is cast only if (r % rows_per_group) < group_counts[r / rows_per_group]
     const int* group_counts;
     int rows_per_group;
+    const int* num_rows_dev;  // optional device int: only rows below it are cast (a count known on the device only)
+    uint8_t* sf_atoms;        // optional: scales go out as UE8M0 scale atoms [ceil(M/128)][hidden/128][512] (power-of-two scales)
 };
 cudaError_t launch_fp8_cast(const Fp8CastArgs& a, cudaStream_t stream);
 

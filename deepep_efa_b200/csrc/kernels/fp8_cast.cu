@@ -20,10 +20,11 @@ __global__ void __launch_bounds__(kCastThreads) fp8_cast_kernel(const Fp8CastArg
     const int row = blockIdx.x * (kCastThreads / 32) + (threadIdx.x >> 5);
     if (row >= a.num_rows) return;
     if (a.group_counts != nullptr && (row % a.rows_per_group) >= a.group_counts[row / a.rows_per_group]) return;  // padding row
+    if (a.num_rows_dev != nullptr && row >= *a.num_rows_dev) return;
     const int H = a.hidden;
     const char* src = reinterpret_cast<const char*>(a.x) + (size_t)row * H * 2;
     uint8_t* dst = a.out + (size_t)row * H;
-    const bool pow2 = a.round_scale != 0 || a.ue8m0 != 0;
+    const bool pow2 = a.round_scale != 0 || a.ue8m0 != 0 || a.sf_atoms != nullptr;
     for (int c0 = 0; c0 < H; c0 += 512) {
         const int ch = c0 + lane * 16;
         const bool act = ch < H;
@@ -54,7 +55,13 @@ __global__ void __launch_bounds__(kCastThreads) fp8_cast_kernel(const Fp8CastArg
         q.z = (int)pack_e4m3x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
         q.w = (int)pack_e4m3x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
         if (act) *reinterpret_cast<int4*>(dst + ch) = q;
-        if (a.ue8m0) {
+        if (a.sf_atoms != nullptr) {
+            if (act && (lane & 7) == 0) {
+                const uint32_t ex = (__float_as_uint(scale) >> 23) & 0xffu;
+                *reinterpret_cast<uint32_t*>(a.sf_atoms + ((size_t)(row >> 7) * (H / 128) + (ch >> 7)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4) =
+                    ex * 0x01010101u;
+            }
+        } else if (a.ue8m0) {
             // lanes 0,8,16,24 hold the four group scales of this 512-channel step
             const uint32_t ex = (__float_as_uint(scale) >> 23) & 0xffu;
             const uint32_t e0 = __shfl_sync(0xffffffffu, ex, 0), e1 = __shfl_sync(0xffffffffu, ex, 8);

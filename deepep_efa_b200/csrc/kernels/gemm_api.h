@@ -47,6 +47,17 @@ struct GroupedGemmArgs {
     int cta_pairs;            // 1 = two CTAs of a cluster share one 256-row MMA (cta_group::2), each staging half of the B tile
     int* error_flag;          // device int, set non-zero when a bounded pipeline wait ran out
     long long timeout_cycles;
+    // Arrival gating (mode 0): the rows of group g are written by other GPUs while this kernel runs. Before the first tile
+    // of a group is loaded, the loader waits (bounded) until ready[g] >= expected[g]; `ready` is advanced with system-scope
+    // release reductions by the senders, `expected` is rank-local. Both null = no gating.
+    const unsigned long long* ready;
+    const unsigned long long* expected;
+    // Scatter epilogue (mode 0, no swiglu): output row m is not stored to c[m] but to row (row_info[m] & 0xffffff) of the
+    // [rows, n] bf16 matrix at scatter_bases[row_info[m] >> 24] (a peer's symmetric memory or this GPU's); rows whose word
+    // is negative are dropped. Null = ordinary output.
+    const int* row_info;
+    const unsigned long long* scatter_bases;
+    unsigned long long* trace;  // optional [2]: earliest first-tile load / latest epilogue end (global timer, ns)
 };
 
 // Returns cudaErrorInvalidValue for unsupported shapes (divisibility rules are in grouped_gemm.cu).

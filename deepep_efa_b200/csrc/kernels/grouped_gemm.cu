@@ -238,6 +238,19 @@ __device__ __forceinline__ uint32_t make_idesc_mx(int n) {
     return d;
 }
 
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// Orders what this thread observed through ordinary loads (the arrival counter) before its later TMA reads of the rows.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 __device__ __forceinline__ int4 pack8_bf16(const float* o) {
@@ -269,6 +282,25 @@ __device__ __forceinline__ void store_block_coalesced(int4* stage, const int4 (&
         const int row = i * RPI + lane / P, piece = lane % P;
         const int4 v = stage[row * P + (piece ^ (row & (P - 1)))];
         if (row < rows_valid) *reinterpret_cast<int4*>(gbase + (size_t)row * ldc + piece * 8) = v;
+    }
+}
+
+// Same block, but every row goes to its own destination: lane l holds the address of row l (nullptr = drop the row).
+template <int kCols>
+__device__ __forceinline__ void store_block_scattered(int4* stage, const int4 (&regs)[kCols / 8], __nv_bfloat16* my_row_ptr, int lane) {
+    constexpr int P = kCols / 8;
+    constexpr int RPI = 32 / P;
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < P; ++j) stage[lane * P + (j ^ (lane & (P - 1)))] = regs[j];
+    __syncwarp();
+    const unsigned long long mine = reinterpret_cast<unsigned long long>(my_row_ptr);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+        const int row = i * RPI + lane / P, piece = lane % P;
+        const int4 v = stage[row * P + (piece ^ (row & (P - 1)))];
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, mine, row));
+        if (dst != nullptr) *reinterpret_cast<int4*>(dst + piece * 8) = v;
     }
 }
 
@@ -443,10 +475,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             int stage = 0, phase = 0, g = 0;
             int issued = 0;  // stages armed so far (saturating), for the drain on the abort path
+            int gated_group = -1;
+            bool stamped = false;
             TileInfo ti;
             bool ok = true;
             for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
                 decode(tile, g, ti);
+                if (p.ready != nullptr && ti.group != gated_group) {
+                    // the rows of this group come from other GPUs: wait until all of them have landed
+                    const unsigned long long want = p.expected[ti.group];
+                    if (ld_acquire_sys_u64(p.ready + ti.group) < want) {
+                        const long long t0 = clock64();
+                        while (ld_acquire_sys_u64(p.ready + ti.group) < want) {
+                            if (*abort_flag || clock64() - t0 > limit) {
+                                *abort_flag = 1;
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!ok) break;
+                    }
+                    fence_proxy_async();
+                    gated_group = ti.group;
+                }
+                if (p.trace != nullptr && !stamped) {
+                    atomicMin(&p.trace[0], global_timer_ns());
+                    stamped = true;
+                }
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, limit)) {
                         ok = false;
@@ -606,13 +661,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.c);
         const int ldc = p.mode == 0 ? (kSwiGLU ? p.n / 2 : p.n) : p.k;
+        const bool scatter = !kSwiGLU && p.mode == 0 && p.row_info != nullptr;
         for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
             decode(tile, g, ti);
             const int row = ti.c_row + row_in_tile;
             __nv_bfloat16* crow = cbase + (size_t)row * ldc + ti.c_col;
+            // scatter epilogue: this lane's row goes to row (word & 0xffffff) of the matrix at scatter_bases[word >> 24]
+            __nv_bfloat16* scat_ptr = nullptr;
+            if (scatter && row < ti.c_row_end) {
+                const int word = p.row_info[row];
+                if (word >= 0)
+                    scat_ptr = reinterpret_cast<__nv_bfloat16*>(p.scatter_bases[word >> 24]) + (size_t)(word & 0xffffff) * ldc + ti.c_col;
+            }
             if (ti.num_kb == 0) {
-                if (row < ti.c_row_end && half == 0)
-                    for (int c = 0; c < C::kOutCols; c += 8) *reinterpret_cast<int4*>(crow + c) = make_int4(0, 0, 0, 0);
+                __nv_bfloat16* zrow = scatter ? scat_ptr : crow;
+                if (row < ti.c_row_end && half == 0 && zrow != nullptr)
+                    for (int c = 0; c < C::kOutCols; c += 8) *reinterpret_cast<int4*>(zrow + c) = make_int4(0, 0, 0, 0);
                 continue;
             }
             if constexpr (C::kPromote) {
@@ -691,7 +755,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         int4 regs[8];
 #pragma unroll
                         for (int c = 0; c < 64; c += 8) regs[c / 8] = pack8_bf16(&acc[c]);
-                        store_block_coalesced<64>(out_stage, regs, wbase + half * kHalfCols, ldc, rows_valid, lane);
+                        if (scatter) store_block_scattered<64>(out_stage, regs, scat_ptr != nullptr ? scat_ptr + half * kHalfCols : nullptr, lane);
+                        else store_block_coalesced<64>(out_stage, regs, wbase + half * kHalfCols, ldc, rows_valid, lane);
                     }
                 }
             } else {
@@ -764,7 +829,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             regs[i / 8] = pack8_bf16(o);
                             regs[4 + i / 8] = pack8_bf16(o2);
                         }
-                        store_block_coalesced<64>(out_stage, regs, wbase + c, ldc, rows_valid, lane);
+                        if (scatter) store_block_scattered<64>(out_stage, regs, scat_ptr != nullptr ? scat_ptr + c : nullptr, lane);
+                        else store_block_coalesced<64>(out_stage, regs, wbase + c, ldc, rows_valid, lane);
                     }
                 }
                 tc_fence_before();
@@ -778,6 +844,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     }
 
+    if (warp >= 2) {
+        // rows scattered into other GPUs' memory are performed there before this kernel counts as finished
+        if (p.row_info != nullptr) __threadfence_system();
+        if (p.trace != nullptr && warp == 2 && lane == 0) atomicMax(&p.trace[1], global_timer_ns());
+    }
     tc_fence_before();
     __syncthreads();
     if constexpr (kPair) cluster_sync_all();  // neither CTA leaves while the other may still signal it or read its operands

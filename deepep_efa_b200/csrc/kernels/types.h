@@ -10,6 +10,7 @@ constexpr int kMaxRanks = 8;            // one NVSwitch domain
 constexpr int kMaxLocalExperts = 1024;  // same cap as the reference (configs.cuh:6)
 constexpr int kMaxTopk = 32;
 constexpr int kMaxVirtualRanks = 8;     // ranks emulated inside one launch (single-GPU test mode)
+constexpr int kMaxFusedExperts = 2048;  // experts of the whole group in the expert-major (fused MoE) dispatch
 
 // Error codes written to the status word (the host decodes them in csrc/host/runtime.hpp).
 enum Status : int {
@@ -25,6 +26,7 @@ enum Status : int {
     kBadArgument = 9,
     kTimeoutTest = 10,
     kBadPeerAccess = 11,  // debug bounds check: a row address fell outside the peer's symmetric buffer (access skipped)
+    kTimeoutFusedNotify = 12,
 };
 
 // Written by kernels into mapped pinned host memory; read by the host after collective calls.
@@ -76,6 +78,12 @@ struct alignas(128) ControlBlock {
     uint64_t ll_data_arrived[2][kMaxRanks];                // monotonically growing row counters
     uint64_t ll_combine_arrived[2][kMaxRanks];
     int ll_mask[kMaxRanks];                                // 1 = rank is masked out (shrink mode)
+    // expert-major dispatch (fused MoE layer): row r = what rank r tells me
+    uint64_t em_seq[kMaxRanks];
+    // two parities (call sequence odd / even): a fast rank may start its next exchange while a slow one still reads this one
+    uint64_t em_desc[2][kMaxRanks][4];                     // rank r's receive buffers: rows, scales, row info, combine stage (offsets)
+    int em_counts[2][kMaxRanks][kMaxFusedExperts];         // rank r's selections per GLOBAL expert (every rank gets the whole vector)
+    uint64_t em_arrived[kMaxLocalExperts];                 // rows landed so far per local expert, monotonic; gates the expert GEMM
 };
 
 static_assert(sizeof(ControlBlock) <= (1u << 20), "control block must fit the first MiB of the symmetric buffer");
@@ -104,8 +112,12 @@ struct RankCtx {
 };
 
 // Kernel families; each has its own monotonically growing sequence number on every rank.
+// Rank-local u64 words behind RankCtx::seq: [kNumFamilies] sequences, [2 kinds][2 parities][kMaxRanks] expected low-latency
+// arrivals, [kMaxLocalExperts] expected rows per local expert of the expert-major dispatch.
+constexpr int kFusedExpectedWord0 = 8 + 2 * 2 * kMaxRanks;
 constexpr int kTraceStampsPerSlot = 16;  // trace layout: [family][slot 0 = first CTA, 1 = last CTA][stamp]
 
-enum Family : int { kFamNotify = 0, kFamDispatch = 1, kFamCombine = 2, kFamBarrier = 3, kFamLLDispatch = 4, kFamLLCombine = 5, kNumFamilies = 8 };
+enum Family : int { kFamNotify = 0, kFamDispatch = 1, kFamCombine = 2, kFamBarrier = 3, kFamLLDispatch = 4, kFamLLCombine = 5, kFamFused = 6, kNumFamilies = 8 };
+static_assert(kFusedExpectedWord0 == kNumFamilies + 2 * 2 * kMaxRanks, "layout of the rank-local sequence words");
 
 }  // namespace dx

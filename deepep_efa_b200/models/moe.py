@@ -9,6 +9,12 @@ Two execution paths share the structure:
   gradients (K-grouped mode).
 * **inference (FP8)**: ``forward_fp8`` quantises inside the dispatch kernel, runs block-scaled FP8 grouped GEMMs
   with the SwiGLU fused into the first GEMM's epilogue, and combines in BF16 (DeepSeek-V3-shaped experts).
+* **fused inference (FP8)**: ``forward_fused`` is the overlapped form of the same computation. The dispatch kernel
+  quantises AND places every (token, expert) row at its final expert-major, 128-row-aligned position in the expert's
+  rank (no permutation pass, no host synchronisation); the first grouped GEMM runs concurrently on the compute stream
+  and starts on an expert as soon as that expert's arrival counter reaches the expected total; the second grouped
+  GEMM's epilogue stores every output row straight into the stage of the token's home rank over NVLink, so the
+  combine that remains is a cross-rank flag exchange and a local weighted sum.
 
 The reference is a communication library only and has no model code; this module is the model-side user of the
 API that the benchmark configurations (fused MoE forward, MoE training step) call for.
@@ -218,6 +224,30 @@ class MoELayer(nn.Module):
         return out
 
 
+    # -- fused FP8 inference path -----------------------------------------------------------------------------------
+    @staticmethod
+    def _C():
+        from .. import _ext
+        return _ext.load()
+
+    def fused_workspace(self, num_tokens: int, capacity_rows: Optional[int] = None) -> "_FusedWorkspace":
+        cache = self.__dict__.setdefault("_fused_ws", {})
+        native = getattr(self, "_mx", None) is not None
+        key = (num_tokens, native)
+        if key not in cache:
+            cache[key] = _FusedWorkspace(self, num_tokens, native, capacity_rows)
+        return cache[key]
+
+    @torch.no_grad()
+    def forward_fused(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
+                      overlap: bool = True) -> torch.Tensor:
+        """Forward only, same arithmetic as :meth:`forward_fp8`, as one overlapped pipeline (see the module docstring).
+        Collective: every rank of the buffer calls it with the same number of tokens. The first call with a new token
+        count allocates the workspace (symmetric memory sized for the worst case)."""
+        if topk_idx is None:
+            topk_idx, topk_weights = self.route(x)
+        return fused_forward_many([self], [x.contiguous()], [topk_idx.contiguous()], [topk_weights.contiguous()], overlap=overlap)[0]
+
     # -- low-latency (decode) path ------------------------------------------------------------------------------
     @torch.no_grad()
     def forward_low_latency(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
@@ -262,6 +292,124 @@ class MoELayer(nn.Module):
             gg.grouped_gemm(w_["hq"], w2, w_["starts"], a_scales=w_["hs"], b_scales=s2, out=y.view(L * N, H), m_ends=ends)
         out, _, _ = buf.low_latency_combine(y, topk_idx, topk_weights, handle, zero_copy=True)
         return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# fused forward: expert-major dispatch -> arrival-gated GEMM1 -> cast -> GEMM2 with scatter epilogue -> local reduce
+# ---------------------------------------------------------------------------------------------------------
+UNIT_ROWS = 8  # rows of one expert a dispatch warp sends between two arrival-counter updates
+
+
+class _FusedWorkspace:
+    """Buffers of one layer for ``num_tokens`` tokens per rank, allocated once: the receive side is sized for the worst
+    case (every selection of every rank lands here), so no step ever needs a host round trip to size anything."""
+
+    def __init__(self, layer: "MoELayer", num_tokens: int, native: bool, capacity_rows: Optional[int] = None) -> None:
+        buf, cfg = layer.buffer, layer.cfg
+        R, L, E, K, H, I = buf.group_size, layer.num_local_experts, cfg.num_experts, cfg.num_topk, cfg.hidden, cfg.intermediate
+        T = num_tokens
+        dev = buf.device
+        worst = R * T * min(K, L) + L * 127
+        rows = worst if capacity_rows is None else capacity_rows
+        self.rows = rows = (rows + 127) // 128 * 128
+        self.num_tokens, self.native = T, native
+        sym = buf.empty_symmetric
+        self.recv_x = sym([rows, H], torch.float8_e4m3fn)
+        # fp32 scales [rows, H/128] or UE8M0 scale atoms [rows/128, H/128, 512]: the same number of bytes
+        self.recv_scales_raw = sym([rows * (H // 128) * 4], torch.uint8)
+        self.recv_scales = (self.recv_scales_raw.view(rows // 128, H // 128, 512) if native
+                            else self.recv_scales_raw.view(torch.float32).view(rows, H // 128))
+        self.recv_info = sym([rows], torch.int32)
+        self.stage = sym([T * K, H], torch.bfloat16)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.my_counts = torch.zeros(E, **i32)
+        self.sel_list = torch.zeros(E * T, **i32)
+        self.send_base = torch.zeros(E, **i32)
+        self.unit_start = torch.zeros(E + 1, **i32)
+        self.m_offsets = torch.zeros(L + 1, **i32)
+        self.m_ends = torch.zeros(L, **i32)
+        self.peer_bases = torch.zeros(4 * R, dtype=torch.int64, device=dev)
+        self.h = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
+        self.hq = torch.empty(rows, I, dtype=torch.float8_e4m3fn, device=dev)
+        self.hs = (torch.empty(rows // 128, I // 128, 512, dtype=torch.uint8, device=dev) if native
+                   else torch.empty(rows, I // 128, dtype=torch.float32, device=dev))
+        C = layer._C()
+        arrived, expected = C.em_gate_words(buf.runtime)
+        self.arrived, self.expected = arrived[:L], expected[:L]
+        self.trace = None
+
+    def enable_trace(self) -> None:
+        """[dispatch first start, dispatch last end, GEMM1 first tile load, GEMM1 last epilogue end] in ns of the GPU's
+        global timer (min / max over the CTAs), for the overlap evidence."""
+        self.trace = torch.zeros(4, dtype=torch.int64, device=self.h.device)
+
+    def reset_trace(self) -> None:
+        big = torch.iinfo(torch.int64).max
+        self.trace.copy_(torch.tensor([big, 0, big, 0], dtype=torch.int64))
+
+
+def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_sms: int = 0):
+    """Fused FP8 forward of one MoE layer on every given rank (one entry per rank: a single entry in a real job, one per
+    emulated rank on a single GPU, where the collectives run as one cooperative launch each and nothing overlaps).
+
+    Streams: the count exchange and the dispatch run on the buffer's communication stream; the expert GEMMs run on the
+    caller's stream as soon as the exchange is done, concurrently with the dispatch, and gate every expert on its arrival
+    counter. The dispatch kernel is launched first and never waits for the GEMM, so the pair cannot deadlock; its small
+    CTAs share the SMs with the GEMM's persistent CTAs."""
+    V = len(layers)
+    l0 = layers[0]
+    C = l0._C()
+    cfg = l0.cfg
+    bufs = [l.buffer for l in layers]
+    rts = [b.runtime for b in bufs]
+    E, K = cfg.num_experts, cfg.num_topk
+    for b in bufs:
+        b.check_status()
+    wss = []
+    for l, x in zip(layers, xs):
+        if l._fp8 is None:
+            l.prepare_fp8()
+        wss.append(l.fused_workspace(x.size(0)))
+    native = wss[0].native
+    cur = torch.cuda.current_stream()
+    comm = bufs[0].comm_stream if (V == 1 and overlap) else cur
+    if comm is not cur:
+        comm.wait_stream(cur)
+    with torch.cuda.stream(comm):
+        C.em_notify(rts, [(i, w.recv_x, w.recv_scales_raw, w.recv_info, w.stage, w.my_counts, w.sel_list, w.send_base, w.unit_start,
+                           w.m_offsets, w.m_ends, w.peer_bases) for i, w in zip(idxs, wss)], E, UNIT_ROWS)
+        planned = torch.cuda.Event()
+        planned.record(comm)
+        sms = num_dispatch_sms or (148 if V == 1 else max(1, 148 // V - 1))
+        C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None,
+                             None if w.trace is None else w.trace[0:2]) for x, w in zip(xs, wss)], E, K, UNIT_ROWS, native, native, sms)
+    if comm is not cur:
+        cur.wait_event(planned)
+    outs = []
+    for l, w in zip(layers, wss):
+        (w13, s13), (w2, s2) = l._fp8
+        R_, L = l.buffer.group_size, l.num_local_experts
+        gate = dict(ready=w.arrived, expected=w.expected, trace=None if w.trace is None else w.trace[2:4])
+        if native:
+            wide = R_ * w.num_tokens * K >= 512 * E
+            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, w.h, 0, 2000.0, w.m_ends, w.recv_scales, l._mx[0 if wide else 2], **gate)
+            C.per_token_cast_to_fp8(w.h, True, False, None, 1, w.hq, w.hs, w.m_offsets[L:], True)
+            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, 2000.0, w.m_ends, w.hs, l._mx[1],
+                           row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
+        else:
+            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, w.recv_scales, s13, w.h, 0, 2000.0, w.m_ends, None, None, **gate)
+            C.per_token_cast_to_fp8(w.h, False, False, None, 1, w.hq, w.hs, w.m_offsets[L:], False)
+            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, w.hs, s2, None, 0, 2000.0, w.m_ends, None, None,
+                           row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
+    # every rank's second GEMM has finished scattering before anybody sums its stage
+    C.barrier(rts)
+    for l, x, i, wt, w in zip(layers, xs, idxs, ws, wss):
+        out = torch.empty(x.size(0), cfg.hidden, dtype=torch.bfloat16, device=x.device)
+        C.stage_reduce(w.stage, out, i, wt, E)
+        outs.append(out)
+    if comm is not cur:
+        cur.wait_stream(comm)  # the dispatch kernel has read x before the caller may reuse it
+    return outs
 
 
 def dense_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w13_all: torch.Tensor, w2_all: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,143 @@
+"""Fused MoE forward on emulated ranks (one GPU): expert-major dispatch placement against a host restatement, and the
+whole pipeline (arrival-gated GEMM1, cast, GEMM2 with the scatter epilogue, home-side reduce) against a dense fp32 loop
+over all experts and against the unfused FP8 path, which does the same arithmetic."""
+import pytest
+import torch
+
+from helpers import make_routing, make_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-12)).item()
+
+
+def _setup(R, T, H, I, E, K, native, seed=0, masked=0.05):
+    from deepep_efa_b200.models.moe import MoEConfig, MoELayer
+    from deepep_efa_b200.parallel.virtual import VirtualCluster
+    L = E // R
+    rows = (R * T * min(K, L) + L * 127 + 127) // 128 * 128
+    sym = rows * (H + (H // 128) * 4 + 4) + T * K * H * 2
+    vc = VirtualCluster(R, num_nvl_bytes=(8 << 20) + 3 * sym, timeout_ms=3000)
+    cfg = MoEConfig(hidden=H, intermediate=I, num_experts=E, num_topk=K, init_std=0.05)
+    layers = [MoELayer(cfg, vc.buffers[r], seed=seed) for r in range(R)]
+    for l in layers:
+        l.prepare_fp8(native_block_scaling=native)
+    xs = [make_tokens(T, H, "cuda", seed=seed + 10 + r) for r in range(R)]
+    idxs, ws = [], []
+    for r in range(R):
+        i, w = make_routing(T, E, K, "cuda", seed=seed + 20 + r, masked_fraction=masked)
+        idxs.append(i), ws.append(w)
+    return vc, layers, xs, idxs, ws
+
+
+@pytest.mark.parametrize("R,T,H,E,K,native", [(2, 70, 512, 8, 3, False), (4, 33, 1024, 16, 4, True), (1, 200, 512, 4, 2, False)])
+def test_expert_major_dispatch_places_rows(R, T, H, E, K, native):
+    """After em_notify + em_dispatch every local expert's block holds the quantised rows of (source rank, token order),
+    the row-info words name (source rank, selection), group offsets are 128-aligned and the arrival counters equal the
+    expected totals."""
+    import deepep_efa_b200 as ep
+    from deepep_efa_b200.models.moe import UNIT_ROWS
+    from deepep_efa_b200.reference import oracle
+    vc, layers, xs, idxs, ws = _setup(R, T, H, 256, E, K, native)
+    try:
+        C = ep._ext.load()
+        L = E // R
+        rts = [b.runtime for b in vc.buffers]
+        wss = [l.fused_workspace(T) for l in layers]
+        for rep in range(2):  # the second call reuses every buffer and moves the monotonic counters on
+            C.em_notify(rts, [(i, w.recv_x, w.recv_scales_raw, w.recv_info, w.stage, w.my_counts, w.sel_list, w.send_base, w.unit_start,
+                               w.m_offsets, w.m_ends, w.peer_bases) for i, w in zip(idxs, wss)], E, UNIT_ROWS)
+            dst_rows = [torch.full((T * K,), -1, dtype=torch.int32, device="cuda") for _ in range(R)]
+            C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, dr, None)
+                                for x, w, dr in zip(xs, wss, dst_rows)], E, K, UNIT_ROWS, native, native, 8)
+            torch.cuda.synchronize()
+            for b in vc.buffers:
+                b.check_status()
+            for d in range(R):
+                w = wss[d]
+                offs, ends = w.m_offsets.tolist(), w.m_ends.tolist()
+                assert all(o % 128 == 0 for o in offs)
+                assert torch.equal(w.arrived, w.expected)
+                info = w.recv_info.cpu()
+                rx = w.recv_x.cpu().view(torch.uint8)
+                for le in range(L):
+                    e = d * L + le
+                    row = offs[le]
+                    for src in range(R):
+                        toks, ks = (idxs[src].cpu() == e).nonzero(as_tuple=True)
+                        n = toks.numel()
+                        if n == 0:
+                            continue
+                        q, s = oracle.per_token_cast_to_fp8(xs[src].cpu()[toks], round_scale=native)
+                        assert torch.equal(rx[row:row + n], q.view(torch.uint8)), (d, le, src)
+                        assert torch.equal(info[row:row + n], (src << 24) | (toks * K + ks).int())
+                        assert torch.equal(dst_rows[src].cpu()[(toks * K + ks)], torch.arange(row, row + n, dtype=torch.int32))
+                        if not native:
+                            assert torch.equal(w.recv_scales.cpu()[row:row + n], s)
+                        else:
+                            atoms = w.recv_scales.cpu()
+                            rr = torch.arange(row, row + n)
+                            for kb in (0, H // 128 - 1):
+                                got = atoms[rr // 128, kb, (rr % 32) * 16 + ((rr // 32) % 4) * 4]
+                                want = ((s[:, kb].contiguous().view(torch.int32) >> 23) & 0xff).to(torch.uint8)
+                                assert torch.equal(got, want)
+                        row += n
+                    assert row == ends[le]
+                    if le + 1 < L:
+                        assert offs[le + 1] == (ends[le] + 127) // 128 * 128
+    finally:
+        vc.destroy()
+
+
+@pytest.mark.parametrize("R,T,H,I,E,K,native", [(2, 150, 512, 256, 8, 3, False), (4, 96, 1024, 256, 16, 4, True), (1, 256, 512, 256, 8, 2, True),
+                                                   (1, 1024, 512, 256, 2, 2, True)])
+def test_fused_forward_matches_dense_and_unfused(R, T, H, I, E, K, native):
+    import deepep_efa_b200 as ep
+    from deepep_efa_b200.models.moe import dense_reference, fused_forward_many
+    vc, layers, xs, idxs, ws = _setup(R, T, H, I, E, K, native, seed=3)
+    try:
+        w13_all = torch.cat([l.w13.detach().float() for l in layers])
+        w2_all = torch.cat([l.w2.detach().float() for l in layers])
+        for rep in range(3):
+            outs = fused_forward_many(layers, xs, idxs, ws)
+            torch.cuda.synchronize()
+            for b in vc.buffers:
+                b.check_status(sync=True)
+            assert ep._ext.load().gemm_error(0) == 0
+            for r in range(R):
+                ref = dense_reference(xs[r], idxs[r], ws[r].masked_fill(idxs[r] == -1, 0), w13_all, w2_all)
+                assert torch.isfinite(outs[r].float()).all()
+                assert _rel(outs[r], ref) < 8e-2, (rep, r, _rel(outs[r], ref))
+    finally:
+        vc.destroy()
+
+
+def test_fused_dispatch_overflow_is_reported_not_written():
+    """A receive buffer that is too small for the rows that would land in it: the count exchange sees it on every rank,
+    no row moves, and the host gets a status instead of a stray store."""
+    import deepep_efa_b200 as ep
+    from deepep_efa_b200.buffer import EPTimeoutError
+    from deepep_efa_b200.models.moe import UNIT_ROWS
+    R, T, H, E, K = 2, 64, 512, 4, 2
+    vc, layers, xs, idxs, ws = _setup(R, T, H, 256, E, K, False, masked=0.0)
+    try:
+        C = ep._ext.load()
+        rts = [b.runtime for b in vc.buffers]
+        wss = [l.fused_workspace(T, capacity_rows=128) for l in layers]  # 2 * 64 * 2 selections need far more than 128 rows
+        for w in wss:
+            w.recv_x.view(torch.uint8).fill_(7)
+        C.em_notify(rts, [(i, w.recv_x, w.recv_scales_raw, w.recv_info, w.stage, w.my_counts, w.sel_list, w.send_base, w.unit_start,
+                           w.m_offsets, w.m_ends, w.peer_bases) for i, w in zip(idxs, wss)], E, UNIT_ROWS)
+        C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None, None) for x, w in zip(xs, wss)],
+                      E, K, UNIT_ROWS, False, False, 4)
+        torch.cuda.synchronize()
+        with pytest.raises(EPTimeoutError):
+            vc.buffers[0].check_status()
+        for w in wss:
+            assert (w.recv_x.view(torch.uint8) == 7).all() and w.m_offsets.abs().sum().item() == 0
+        for b in vc.buffers:
+            b.runtime.clear_status()
+    finally:
+        vc.destroy()

@@ -127,12 +127,18 @@ def main(args) -> None:
             result["normal"] = _bench_normal(deep_ep, buf, rank, world, flush, max(10, min(steps, 50)), warmup, B)
         except Exception as e:
             result["normal"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
-    if rank == 0:
-        B.emit(result)
     try:
         buf.destroy()
     except Exception:
         pass
+    if not getattr(args, "skip_moe", False):
+        try:
+            import bench_moe
+            result.update(bench_moe.moe_extras("reference", rank, world, steps=getattr(args, "moe_steps", 5), warmup=3))
+        except Exception as e:
+            result["moe_error"] = f"{type(e).__name__}: {str(e)[:200]}"
+    if rank == 0:
+        B.emit(result)
     dist.destroy_process_group()
 
 

@@ -424,6 +424,13 @@ def run_ours(args):
     if not args.skip_normal:
         normal = bench_normal(buf, rank, world, flush, max(10, min(steps, 50)), warmup)
 
+    buf.destroy()
+    # ---------------- model-level numbers on top of the library (bench_moe.py holds the full versions) ----------------
+    moe = {}
+    if not args.skip_moe:
+        import bench_moe
+        moe = bench_moe.moe_extras("ours", rank, world, steps=args.moe_steps, warmup=3)
+
     result = {
         "metric": "ll_dispatch_combine_us",
         "value": round(ll_us, 3),
@@ -457,9 +464,9 @@ def run_ours(args):
         "normal": normal,
         "impl": "deepep_efa_b200",
     }
+    result.update(moe)
     if rank == 0:
         emit(result)
-    buf.destroy()
     dist.destroy_process_group()
 
 
@@ -532,6 +539,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-normal", action="store_true")
     ap.add_argument("--skip-breakdown", action="store_true")
+    ap.add_argument("--skip-moe", action="store_true", help="leave out the model-level extras (fused MoE forward, decode step, training step)")
+    ap.add_argument("--moe-steps", type=int, default=5)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -156,6 +156,128 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         buf.check_status()
         assert rel(yl, ref.detach()) < 8e-2, rel(yl, ref.detach())
+        # ---- the fused pipeline with real overlap: dispatch on the communication stream, gated GEMM on this one ----
+        for native in (False, True):
+            layer.prepare_fp8(native_block_scaling=native)
+            for rep in range(3):
+                align()
+                yf = layer.forward_fused(xm.detach(), mi, mw)
+                torch.cuda.synchronize()
+                buf.check_status(sync=True)
+                assert rel(yf, ref.detach()) < 8e-2, (native, rep, rel(yf, ref.detach()))
+        buf.destroy()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+
+
+def _worker_pressure(rank, world, port, q):
+    """Full-size low-latency shape, 3 seeds x 20 repeats: every repeat of a seed must reproduce the first one bit for bit
+    (received rows, counts, source info, combined output), in the staged and in the zero-copy (pull) form."""
+    import traceback
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import deepep_efa_b200 as ep
+        from deepep_efa_b200.reference import oracle
+        from helpers import make_routing, make_tokens
+        T, H, E, K = 128, 7168, 256, 8
+        L = E // world
+        buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=2 << 20, num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(T, H, world, E),
+                        low_latency_mode=True, explicitly_destroy=True, timeout_ms=20000)
+        for seed in range(3):
+            x = make_tokens(T, H, "cuda", seed=100 * seed + rank)
+            idx, w = make_routing(T, E, K, "cuda", seed=100 * seed + rank, masked_fraction=0.02)
+            first = None
+            for rep in range(20):
+                (px, ps), cnt, h, _, _ = buf.low_latency_dispatch(x, idx, T, E, use_fp8=True)
+                valid = torch.arange(px.size(1), device="cuda")[None, :] < cnt[:, None]
+                sig = [oracle.hash_tensor(px.view(torch.uint8)[valid]), oracle.hash_tensor(ps[valid]), oracle.hash_tensor(cnt),
+                       oracle.hash_tensor(h[0][valid]), oracle.hash_tensor(h[1])]
+                y = oracle.per_token_cast_back(px.view(-1, H), ps.view(-1, H // 128)).view(px.shape)
+                zero_copy = rep % 2 == 1
+                if zero_copy:
+                    buf.get_next_low_latency_combine_buffer(h).copy_(y)
+                o, _, _ = buf.low_latency_combine(y, idx, w, h, zero_copy=zero_copy)
+                sig.append(oracle.hash_tensor(o))
+                torch.cuda.synchronize()
+                buf.check_status()
+                if first is None:
+                    first = sig
+                    want = x.float() * w.masked_fill(idx == -1, 0).sum(dim=1, keepdim=True)
+                    assert oracle.calc_diff(want, o.float()) < 9e-4
+                assert sig == first, f"seed {seed} repeat {rep}: results differ from the first repeat"
+        buf.destroy()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+
+
+def _worker_shrink(rank, world, port, q):
+    """Shrink mode with a host-made failure: rank 0 simply does not take part in one step (it sits in a host barrier, no
+    kernel of this library in flight). The others' waits run out after a short limit, they mask rank 0 on the device,
+    finish the step among themselves, and keep working; a collective recover() brings rank 0 back."""
+    import traceback
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import deepep_efa_b200 as ep
+        from deepep_efa_b200.buffer import EPTimeoutError
+        from deepep_efa_b200.reference import oracle
+        from helpers import make_routing, make_tokens
+        T, H, E, K = 32, 1024, 4 * world, 4
+        L = E // world
+        buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=2 << 20, num_rdma_bytes=ep.Buffer.get_low_latency_rdma_size_hint(T, H, world, E),
+                        low_latency_mode=True, explicitly_destroy=True, enable_shrink=True, timeout_ms=300)
+        x = make_tokens(T, H, "cuda", seed=rank)
+        idx, w = make_routing(T, E, K, "cuda", seed=rank)
+
+        def step(expect_timeout=False):
+            rx, cnt, h, _, _ = buf.low_latency_dispatch(x, idx, T, E, use_fp8=False)
+            o, _, _ = buf.low_latency_combine(rx.clone(), idx, w, h)
+            torch.cuda.synchronize()
+            if expect_timeout:
+                with pytest.raises(EPTimeoutError):
+                    buf.check_status()
+                buf.runtime.clear_status()
+            else:
+                buf.check_status()
+            return o
+
+        def want(masked=()):
+            keep = idx >= 0
+            for m in masked:
+                keep = keep & (idx // L != m)
+            return x.float() * (w * keep).sum(dim=1, keepdim=True)
+
+        torch.cuda.synchronize()
+        dist.barrier()
+        assert oracle.calc_diff(want(), step().float()) < 1e-5          # everybody takes part
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank != 0:
+            o = step(expect_timeout=True)                                 # rank 0 is silent: the waits run out, it gets masked
+            st = torch.zeros(world, dtype=torch.int32, device="cuda")
+            buf.low_latency_query_mask_buffer(st)
+            assert st.tolist() == [1] + [0] * (world - 1), st.tolist()
+            assert oracle.calc_diff(want(masked=(0,)), o.float()) < 1e-5
+            o = step()                                                    # the survivors carry on without waiting for it
+            assert oracle.calc_diff(want(masked=(0,)), o.float()) < 1e-5
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.low_latency_clean_mask_buffer()
+        buf.recover()                                                     # collective: sequence state starts over on every rank
+        assert oracle.calc_diff(want(), step().float()) < 1e-5
         buf.destroy()
         dist.destroy_process_group()
         q.put((rank, "ok"))
@@ -283,6 +405,20 @@ def _run_ranks(target, world, extra=()):
     for rank, msg in res:
         assert msg == "ok", f"rank {rank}: {msg}"
     assert len(res) == world, f"only {len(res)} of {world} ranks reported"
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_low_latency_pressure_hash_equality(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run_ranks(_worker_pressure, world)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_shrink_mode_masks_a_silent_rank(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run_ranks(_worker_shrink, world)
 
 
 @pytest.mark.parametrize("world,P", [(2, 1), (4, 2)])

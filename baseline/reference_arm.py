@@ -190,6 +190,20 @@ def _bench_normal(deep_ep, buf, rank, world, flush, steps, warmup, B):
         gbps = n_recv * H * 2 / 1e9 / (ms / 1e3)
         if "combine_bf16" not in best or gbps > best["combine_bf16"]["GBps"]:
             best["combine_bf16"] = {"ms": round(ms, 4), "GBps": round(gbps, 1), "chunk": chunk}
+    # the same two kernels at this library's default grid size (32 SMs), best chunk of the sweeps above
+    try:
+        deep_ep.Buffer.set_num_sms(32)
+        cfg_d = deep_ep.Config(32, best["dispatch_fp8_cached"]["chunk"], 256)
+        cfg_c = deep_ep.Config(32, best["combine_bf16"]["chunk"], 256)
+        for name, fn, nbytes in (("dispatch_fp8_cached_32sms", lambda: buf.dispatch(x_e4m3, handle=handle_ref, config=cfg_d), n_recv * H * 2 * (1 + 4 / 128) / 2),
+                                 ("combine_bf16_32sms", lambda: buf.combine(y, handle_ref, config=cfg_c), n_recv * H * 2)):
+            for _ in range(warmup):
+                fn()
+            ms = B.max_over_ranks(B.timed_loop(fn, steps, flush))
+            best[name] = {"ms": round(ms, 4), "GBps": round(nbytes / 1e9 / (ms / 1e3), 1)}
+    except Exception as e:
+        best["equal_budget_error"] = f"{type(e).__name__}: {str(e)[:200]}"
+    deep_ep.Buffer.set_num_sms(24)
     best["recv_tokens"] = int(n_recv)
     best["note"] = "24 SMs, best NVL chunk of a small sweep (the reference's own tuning protocol, tests/test_intranode.py:200-262)"
     return best

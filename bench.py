@@ -491,6 +491,22 @@ def bench_normal(buf, rank, world, flush, steps, warmup):
     do_dispatch()
     (rx, rs), _, _, _, handle, _ = state["r"]
     n_recv = rx.size(0)
+    # correctness of what is timed (the reference's check, tests/test_intranode.py:80-86): a payload that is constant per
+    # source rank must arrive as one constant segment per source, and combining it must give x * (ranks the token went to)
+    xc = torch.full((NORMAL_TOKENS, HIDDEN), float(rank + 1), dtype=torch.bfloat16, device="cuda")
+    rc, *_ = buf.dispatch(xc, handle=handle)
+    rpm = handle[0].cpu()
+    start = 0
+    for src in range(world):
+        end = int(rpm[src, rank])
+        seg = rc[start:end]
+        assert seg.numel() == 0 or (float(seg.float().min()) == src + 1 and float(seg.float().max()) == src + 1), f"rows of source {src} are wrong"
+        start = end
+    assert start == n_recv
+    back, _, _ = buf.combine(rc, handle)
+    hits = in_rank.sum(dim=1, keepdim=True).float()
+    assert torch.equal(back.float(), xc.float() * hits), "combine(dispatch(x)) != x * hits"
+    del rc, back
     y = buf.empty_symmetric([n_recv, HIDDEN], torch.bfloat16)
     y.normal_()
 
@@ -515,6 +531,17 @@ def bench_normal(buf, rank, world, flush, steps, warmup):
         if name.startswith("dispatch"):
             nbytes = nbytes * (1 + 4 / 128) / 2
         res[name] = {"ms": round(ms, 4), "GBps": round(nbytes / 1e9 / (ms / 1e3), 1)}
+    # the same kernels at the reference's SM budget (24), next to the default grid above
+    cfg24 = ep.Config(24, 6, 256, 6, 128)
+    for name, fn in (("dispatch_fp8_cached_prequantized_24sms", lambda: state.__setitem__("p", buf.dispatch(xq, handle=handle, config=cfg24))),
+                     ("combine_bf16_24sms", lambda: state.__setitem__("o", buf.combine(y, handle, config=cfg24)))):
+        for _ in range(warmup):
+            fn()
+        ms = max_over_ranks(timed_loop(fn, steps, flush))
+        nbytes = n_recv * HIDDEN * 2 * ((1 + 4 / 128) / 2 if name.startswith("dispatch") else 1)
+        res[name] = {"ms": round(ms, 4), "GBps": round(nbytes / 1e9 / (ms / 1e3), 1)}
+    res["default_num_sms"] = {"dispatch": ep.Buffer.get_dispatch_config(world).num_sms, "combine": ep.Buffer.get_combine_config(world).num_sms}
+    res["checked"] = "constant-per-source payload arrives as one segment per source; combine(dispatch(x)) == x * hits"
     buf.check_status(sync=True)
     res["recv_tokens"] = int(n_recv)
     res["bytes_definition"] = "recv_x.numel()*2 (x(1+4/128)/2 for FP8), all source ranks including self"

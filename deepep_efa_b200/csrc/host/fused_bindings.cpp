@@ -78,7 +78,7 @@ void em_notify(std::vector<py::object> rts, std::vector<py::tuple> per_rank, int
         DXF_CHECK(T * K < (1 << 24), "too many selections per rank (T*K must stay below 2^24)");
         const auto dev = topk_idx.device();
         DXF_CHECK(i32_on(my_counts, dev, num_experts) && i32_on(sel_list, dev, (int64_t)num_experts * T) && i32_on(send_base, dev, num_experts) &&
-                      i32_on(unit_start, dev, num_experts + 1) && i32_on(m_offsets, dev, L + 1) && i32_on(m_ends, dev, L),
+                      i32_on(unit_start, dev, num_experts + 2) && i32_on(m_offsets, dev, L + 1) && i32_on(m_ends, dev, L),
                   "em_notify: plan tensors must be int32 on this rank's GPU with the documented sizes");
         DXF_CHECK(peer_bases.is_cuda() && peer_bases.device() == dev && peer_bases.element_size() == 8 && peer_bases.is_contiguous() && peer_bases.numel() >= 4 * R,
                   "peer_bases must be 64-bit [4, R]");
@@ -99,6 +99,7 @@ void em_notify(std::vector<py::object> rts, std::vector<py::tuple> per_rank, int
         a.sel_list = sel_list.data_ptr<int>();
         a.send_base = send_base.data_ptr<int>();
         a.unit_start = unit_start.data_ptr<int>();
+        a.unit_counter = unit_start.data_ptr<int>() + num_experts + 1;  // the tensor's last int is the hand-out counter
         a.m_offsets = m_offsets.data_ptr<int>();
         a.m_ends = m_ends.data_ptr<int>();
         a.peer_bases = reinterpret_cast<uint64_t*>(peer_bases.data_ptr());
@@ -130,7 +131,7 @@ void em_dispatch(std::vector<py::object> rts, std::vector<py::tuple> per_rank, i
         const int64_t T = x.size(0);
         const auto dev = x.device();
         DXF_CHECK(i32_on(my_counts, dev, num_experts) && i32_on(sel_list, dev, (int64_t)num_experts * T) && i32_on(send_base, dev, num_experts) &&
-                      i32_on(unit_start, dev, num_experts + 1), "em_dispatch: plan tensors do not match");
+                      i32_on(unit_start, dev, num_experts + 2), "em_dispatch: plan tensors do not match");
         DXF_CHECK(peer_bases.is_cuda() && peer_bases.device() == dev && peer_bases.element_size() == 8 && peer_bases.numel() >= 4 * core->num_ranks(), "peer_bases must be 64-bit [4, R]");
         dx::EmDispatchArgs& a = args[v];
         a.ctx = core->ctx();
@@ -146,6 +147,7 @@ void em_dispatch(std::vector<py::object> rts, std::vector<py::tuple> per_rank, i
         a.sel_list = sel_list.data_ptr<int>();
         a.send_base = send_base.data_ptr<int>();
         a.unit_start = unit_start.data_ptr<int>();
+        a.unit_counter = unit_start.data_ptr<int>() + num_experts + 1;
         a.peer_bases = reinterpret_cast<const uint64_t*>(peer_bases.data_ptr());
         a.dst_row = nullptr;
         if (!t[6].is_none()) {

@@ -63,7 +63,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
                            c10::optional<torch::Tensor> sfa_atoms, c10::optional<torch::Tensor> sfb_atoms,
                            c10::optional<torch::Tensor> ready, c10::optional<torch::Tensor> expected,
                            c10::optional<torch::Tensor> row_info, c10::optional<torch::Tensor> scatter_bases,
-                           c10::optional<torch::Tensor> trace) {
+                           c10::optional<torch::Tensor> trace, bool mn_major) {
     DXG_CHECK(a.is_cuda() && b.is_cuda() && m_offsets.is_cuda(), "operands must be CUDA tensors");
     DXG_CHECK(a.is_contiguous() && b.is_contiguous() && m_offsets.is_contiguous(), "operands must be contiguous");
     DXG_CHECK(m_offsets.scalar_type() == torch::kInt32 && m_offsets.dim() == 1 && m_offsets.numel() >= 2, "m_offsets must be int32 [G+1]");
@@ -89,11 +89,14 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
     p.swiglu = swiglu ? 1 : 0;
     torch::Tensor c;
     auto bf16 = a.options().dtype(torch::kBFloat16);
+    DXG_CHECK(!mn_major || (!fp8 && !swiglu), "MN-major operands are bf16 only, without swiglu");
     if (mode == 0) {
         const int64_t M = a.size(0), K = a.size(1);
         DXG_CHECK(b.numel() % ((int64_t)G * K) == 0, "B must be [G, N, K]");
         const int64_t N = b.numel() / ((int64_t)G * K);
-        DXG_CHECK(b.size(-1) == K, "B's last dimension must equal K");
+        // MN-major B is [G, K, N]: the forward weight read as the operand of the input-gradient GEMM
+        DXG_CHECK(mn_major ? (b.dim() == 3 && b.size(1) == K && b.size(2) == N) : b.size(-1) == K, "B's reduction dimension must equal K");
+        p.b_mn = mn_major ? 1 : 0;
         DXG_CHECK(!swiglu || N % 2 == 0, "swiglu needs an even N (gate and up stacked)");
         const int64_t out_cols = swiglu ? N / 2 : N;
         // with the scatter epilogue nothing is stored to `c`: every row goes to the address its row_info word names
@@ -124,8 +127,11 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         }
     } else {
         DXG_CHECK(mode == 1 && !fp8 && !swiglu, "K-grouped mode is bf16 only, without swiglu");
-        DXG_CHECK(b.dim() == 2 && a.size(1) == b.size(1), "mode 1: A [N_out, M] and B [K_out, M] must share M");
-        const int64_t n_out = a.size(0), k_out = b.size(0), M = a.size(1);
+        // ordinary: A [N_out, M], B [K_out, M]; MN-major: A [M, N_out], B [M, K_out] (gradient and activation as they are)
+        const int md = mn_major ? 0 : 1;
+        DXG_CHECK(b.dim() == 2 && a.size(md) == b.size(md), "mode 1: A and B must share M");
+        const int64_t n_out = a.size(1 - md), k_out = b.size(1 - md), M = a.size(md);
+        p.a_mn = p.b_mn = mn_major ? 1 : 0;
         c = out.has_value() ? *out : torch::empty({(int64_t)G, n_out, k_out}, bf16);
         DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && c.numel() == (int64_t)G * n_out * k_out, "out must be contiguous bf16 [G, N_out, K_out]");
         p.m_total = (int)M;
@@ -150,7 +156,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         const char* pr = std::getenv("DEEPEP_GEMM_PAIR");
         if (pr != nullptr && (pr[0] == '0' || pr[0] == '1')) p.cta_pairs = pr[0] == '1';
         else p.cta_pairs = (!fp8 && p.m_ends == nullptr && (mode == 1 || (int64_t)p.m_total >= 1024 * (int64_t)G)) ? 1 : 0;
-        if (p.num_sms < 2) p.cta_pairs = 0;
+        if (p.num_sms < 2 || mn_major) p.cta_pairs = 0;
     }
     if (ready.has_value() || expected.has_value()) {
         DXG_CHECK(mode == 0 && ready.has_value() && expected.has_value(), "ready and expected go together (M-grouped mode)");
@@ -168,7 +174,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         p.scatter_bases = reinterpret_cast<const unsigned long long*>(scatter_bases->data_ptr());
     }
     if (trace.has_value()) {
-        DXG_CHECK(trace->element_size() == 8 && trace->is_contiguous() && trace->numel() >= 2, "trace must be 64-bit [2]");
+        DXG_CHECK(trace->element_size() == 8 && trace->is_contiguous() && trace->numel() >= 4, "trace must be 64-bit [4]");
         p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr());
     }
     p.error_flag = error_flag(device).data_ptr<int>();
@@ -328,7 +334,7 @@ void bind_gemm(py::module_& m) {
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
           py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none(), py::arg("sfa_atoms") = py::none(), py::arg("sfb_atoms") = py::none(),
           py::arg("ready") = py::none(), py::arg("expected") = py::none(), py::arg("row_info") = py::none(),
-          py::arg("scatter_bases") = py::none(), py::arg("trace") = py::none());
+          py::arg("scatter_bases") = py::none(), py::arg("trace") = py::none(), py::arg("mn_major") = false);
     m.def("build_plan", &build_plan);
     m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
     m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());

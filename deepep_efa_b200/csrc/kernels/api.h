@@ -147,6 +147,7 @@ struct EmNotifyArgs {
     int* sel_list;                // [E, T] selection ids (t*K + k) of every expert in token order
     int* send_base;               // [E] row of my first selection of expert e inside e's rank
     int* unit_start;              // [E+1] exclusive prefix of work units in send order (local expert major, rank minor)
+    int* unit_counter;            // [1] next work unit of the dispatch kernel, reset here
     int* m_offsets;               // [L+1] 128-aligned first row of my local experts; [L] = rows in use
     int* m_ends;                  // [L] end of the valid rows of every local expert
     uint64_t* peer_bases;         // [4, R] device pointers of every rank's rows / scales / info / stage
@@ -163,6 +164,7 @@ struct EmDispatchArgs {
     const int* sel_list;
     const int* send_base;
     const int* unit_start;
+    int* unit_counter;            // [1] next unit to hand out (zeroed by the count exchange)
     const uint64_t* peer_bases;
     int* dst_row;                 // [T*K] or nullptr: row each selection was stored to (entries of unselected slots untouched)
     int num_sms;

@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(kEmNotifyThreads, 1) em_notify_kernel(const __
         if (overflow) {
             if (tid == 0) report(c.status, kBadArgument, me, -1, s_rank_rows[me]);
             for (int i = tid; i <= E; i += kEmNotifyThreads) a.unit_start[i] = 0;
+            if (tid == 0) *a.unit_counter = 0;
             for (int le = tid; le <= L; le += kEmNotifyThreads) {
                 a.m_offsets[le] = 0;
                 if (le < L) a.m_ends[le] = 0;
@@ -160,6 +161,7 @@ __global__ void __launch_bounds__(kEmNotifyThreads, 1) em_notify_kernel(const __
             }
             if (lane == 0) a.unit_start[E] = carry;
         }
+        if (tid == 0) *a.unit_counter = 0;
         if (tid < 4 * R) {
             const int which = tid / R, r = tid % R;
             a.peer_bases[tid] = reinterpret_cast<uint64_t>(c.at<char>(r, ld_relaxed_sys(&my->em_desc[P][r][which])));
@@ -199,15 +201,18 @@ __global__ void __launch_bounds__(kEmDispatchThreads, 6) em_dispatch_kernel(cons
     __syncthreads();
     if (a.trace != nullptr && tid == 0) atomicMin(&a.trace[0], global_timer());
     const int total_units = s_unit_start[E];
-    const int total_warps = gridDim.x * kEmDispatchWarps;
     const int num_kb = H / 128;
     char* const* rows_base = reinterpret_cast<char* const*>(a.peer_bases);
     char* const* scales_base = reinterpret_cast<char* const*>(a.peer_bases + R);
     int* const* info_base = reinterpret_cast<int* const*>(a.peer_bases + 2 * R);
 
-    // Units are dealt round-robin over (CTA, warp) with the CTA index fastest, so that at any moment the whole grid works
-    // on neighbouring units: experts complete in order.
-    for (int u = warp * gridDim.x + blockIdx.x; u < total_units; u += total_warps) {
+    // Units are handed out through one counter (reset by the count exchange), so they are taken in order by whichever warps
+    // are running: experts complete in order even when only part of the grid is resident next to a GEMM.
+    while (true) {
+        int u = 0;
+        if (lane == 0) u = atomicAdd(a.unit_counter, 1);
+        u = __shfl_sync(0xffffffffu, u, 0);
+        if (u >= total_units) break;
         int lo = 0, hi = E;  // largest o with unit_start[o] <= u
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;

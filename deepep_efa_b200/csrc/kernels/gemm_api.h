@@ -57,7 +57,14 @@ struct GroupedGemmArgs {
     // is negative are dropped. Null = ordinary output.
     const int* row_info;
     const unsigned long long* scatter_bases;
-    unsigned long long* trace;  // optional [2]: earliest first-tile load / latest epilogue end (global timer, ns)
+    unsigned long long* trace;  // optional [4]: earliest first-tile load / latest epilogue end (global timer, ns) / first wait that
+                                // gave up (role << 56 | tile << 24 | k block << 8 | slot; 0 = none) / what the loader was doing
+                                // then (state << 32 | tile; state 1 = arrival gate, 2 = waiting for a free stage, 3 = loads issued)
+    // MN-major operands (bf16, no swiglu): the operand is read from a tensor whose contiguous dimension is the operand's row
+    // index instead of K, so gradients need no transposed copies. mode 0: b_mn = 1, B given as [G, K, N] (input gradients:
+    // the forward weight as it is). mode 1: a_mn = b_mn = 1, A given as [M_total, N_out], B as [M_total, K_out] (weight
+    // gradients: output gradient and activation as they are).
+    int a_mn, b_mn;
 };
 
 // Returns cudaErrorInvalidValue for unsupported shapes (divisibility rules are in grouped_gemm.cu).

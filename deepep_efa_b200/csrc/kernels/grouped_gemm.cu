@@ -58,17 +58,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: returns false (and raises the CTA abort flag) when the limit runs out or another role
 // has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit) {
+// `note` (optional, device memory) keeps the first wait that gave up: `what` = (role code << 56 | tile << 24 | k block << 8 | slot).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit,
+                                          unsigned long long* note = nullptr, unsigned long long what = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
         if (clock64() - t0 > limit) {
             *abort_flag = 1;
+            if (note != nullptr) atomicCAS(note, 0ull, what);
             return false;
         }
     }
     return true;
+}
+__device__ __forceinline__ unsigned long long wait_id(int role, int tile, int kb, int slot) {
+    return ((unsigned long long)role << 56) | ((unsigned long long)(tile & 0xffffffff) << 24) | ((unsigned long long)(kb & 0xffff) << 8) |
+           (unsigned long long)(slot & 0xff);
 }
 
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
@@ -135,13 +142,27 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: fp32 accumulate, A and B K-major, M = 128, N = n.
+// MN-major operand tile (the tensor's contiguous dimension is the tile's row index, not K): the tile is stored as chunks of
+// 64 rows; a chunk is 64 K-steps of 128 bytes (64 BF16 row elements), 128B-swizzled in groups of 8 K-steps. Stride byte
+// offset = distance between 8-K-step groups (1024), leading byte offset = distance between 64-row chunks (8192).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(8192 >> 4) << 16;              // leading byte offset: next 64-row chunk
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: next group of 8 K-steps
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp32 accumulate, M = 128, N = n; bit 15 / 16 = A / B is MN-major instead of K-major.
 template <bool kFp8>
-__device__ __forceinline__ uint32_t make_idesc(int n, int m = kBlockM) {
+__device__ __forceinline__ uint32_t make_idesc(int n, int m = kBlockM, int a_mn = 0, int b_mn = 0) {
     uint32_t d = 0;
     d |= 1u << 4;                          // D format = F32
     d |= (kFp8 ? 0u : 1u) << 7;            // A format: E4M3 (f8f6f4) or BF16 (f16)
     d |= (kFp8 ? 0u : 1u) << 10;           // B format
+    d |= (a_mn ? 1u : 0u) << 15;           // A major
+    d |= (b_mn ? 1u : 0u) << 16;           // B major
     d |= (uint32_t)(n >> 3) << 17;         // N / 8
     d |= (uint32_t)(m >> 4) << 24;         // M / 16 (256 for a CTA pair)
     return d;
@@ -308,6 +329,8 @@ struct TileInfo {
     int a_row, a_k0, b_row, b_row2, b_k0, num_kb, c_row, c_col, group, nblock, nblock2;
     int c_row_end;  // first output row this tile must not write (end of its group; groups need no 128-row alignment)
     int nt;         // n-tile index inside the group (kMx: selects the B scale atoms)
+    // MN-major operands: first tile row inside the tensor's contiguous dimension, and the tensor row of K index 0
+    int a_mn0, a_kbase, b_mn0, b_kbase;
 };
 
 template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
@@ -362,6 +385,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int* tile_start = reinterpret_cast<int*>(bars + 32);  // [G+1] first tile index of every group
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ volatile int s_prod_state[2];  // what the loader is doing (1 = arrival gate, 2 = free stage, 3 = loads issued) and for which tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.num_groups;
@@ -410,6 +434,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int total_tiles = tile_start[G];
     volatile int* abort_flag = &s_abort;
     const long long limit = p.timeout_cycles;
+    unsigned long long* note = p.trace != nullptr ? p.trace + 2 : nullptr;  // trace[2]: first bounded wait that gave up
 
     // Decodes tile index -> coordinates; `g` is a cursor that only moves forward.
     auto decode = [&](int tile, int& g, TileInfo& ti) {
@@ -425,6 +450,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int mt = p.tile_order == 0 ? local % tiles_m : local / tiles_n_;
             ti.a_row = m0 + mt * C::kTileRows + (int)cta_rank * kBlockM;
             ti.nt = nt;
+            ti.a_mn0 = ti.a_kbase = 0;                                          // mode 0: A is always K-major
+            ti.b_mn0 = nt * kBlockN + (int)cta_rank * (kBlockN / 2);            // MN-major B: [G * K, N], N contiguous
+            ti.b_kbase = g * p.k;
             ti.a_k0 = 0;
             ti.b_k0 = 0;
             ti.num_kb = p.k / elem_per_kb;
@@ -450,6 +478,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ti.a_row = it * C::kTileRows + (int)cta_rank * kBlockM;
             ti.b_row = jt * kBlockN + (int)cta_rank * (kBlockN / 2);
             ti.b_row2 = 0;
+            ti.a_mn0 = ti.a_row;                                                // MN-major: A is [M, N_out], B is [M, K_out]
+            ti.b_mn0 = ti.b_row;
+            ti.a_kbase = ti.b_kbase = m0;
             ti.a_k0 = m0;
             ti.b_k0 = m0;
             ti.num_kb = (m1 - m0) / elem_per_kb;
@@ -481,13 +512,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int tile = sched_id; tile < total_tiles && ok; tile += sched_stride) {
                 decode(tile, g, ti);
+                s_prod_state[1] = tile;
                 if (p.ready != nullptr && ti.group != gated_group) {
+                    s_prod_state[0] = 1;
                     // the rows of this group come from other GPUs: wait until all of them have landed
                     const unsigned long long want = p.expected[ti.group];
                     if (ld_acquire_sys_u64(p.ready + ti.group) < want) {
                         const long long t0 = clock64();
                         while (ld_acquire_sys_u64(p.ready + ti.group) < want) {
                             if (*abort_flag || clock64() - t0 > limit) {
+                                if (!*abort_flag && note != nullptr) atomicCAS(note, 0ull, wait_id(2, tile, 0, ti.group));
                                 *abort_flag = 1;
                                 ok = false;
                                 break;
@@ -503,7 +537,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     stamped = true;
                 }
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, limit)) {
+                    s_prod_state[0] = 2;
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, limit, note, wait_id(1, tile, kb, stage))) {
                         ok = false;
                         break;
                     }
@@ -523,6 +558,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         continue;
                     }
+                    s_prod_state[0] = 3;
                     mbar_expect_tx(&full[stage], C::kStageTxBytes);
                     if constexpr (kMx) {
                         // scale atoms: [row tile][K block][512] for A, [group][n tile][K block][512] for B
@@ -531,6 +567,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         bulk_load_1d(ssf, p.sfa_atoms + ((size_t)(ti.a_row >> 7) * nkb + kb) * 512, 512, &full[stage]);
                         bulk_load_1d(ssf + 512, p.sfb_atoms + (((size_t)ti.group * (p.n / kBlockN) + ti.nt) * nkb + kb) * (512 * C::kSfBAtoms),
                                      512 * C::kSfBAtoms, &full[stage]);
+                    }
+                    if constexpr (!kFp8 && !kSwiGLU && !kMx) {
+                        if (p.a_mn | p.b_mn) {
+                            // an MN-major tile arrives as chunks of 64 rows x 64 K-steps (8 KiB each)
+                            if (p.a_mn) {
+#pragma unroll
+                                for (int j = 0; j < kBlockM / 64; ++j)
+                                    tma_load_2d(&map_a, &full[stage], sa + j * 8192, ti.a_mn0 + j * 64, ti.a_kbase + kb * 64);
+                            } else {
+                                tma_load_2d(&map_a, &full[stage], sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
+                            }
+                            if (p.b_mn) {
+#pragma unroll
+                                for (int j = 0; j < kBlockN / 64; ++j)
+                                    tma_load_2d(&map_b, &full[stage], sb + j * 8192, ti.b_mn0 + j * 64, ti.b_kbase + kb * 64);
+                            } else {
+                                tma_load_2d(&map_b, &full[stage], sb, ti.b_k0 + kb * elem_per_kb, ti.b_row);
+                            }
+                            if (issued < C::kStages) ++issued;
+                            if (++stage == C::kStages) {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                            continue;
+                        }
                     }
                     tma_load_2d(&map_a, &full[stage], sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
                     if (kSwiGLU) {
@@ -572,7 +633,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0 && cta_rank == 0) {
-            const uint32_t idesc = kMx ? make_idesc_mx(kBlockN) : make_idesc<kFp8>(kBlockN, C::kTileRows);
+            const uint32_t idesc = kMx ? make_idesc_mx(kBlockN) : make_idesc<kFp8>(kBlockN, C::kTileRows, p.a_mn, p.b_mn);
+            // bytes (in 16-byte units) one K = 16 step moves the operand's start address: 32 B inside the swizzle atom when K
+            // is contiguous, 16 K-steps of 128 B when the rows are
+            const uint64_t a_kstep = p.a_mn ? 128 : 2, b_kstep = p.b_mn ? 128 : 2;
             int sf_buf = 0;
             int stage = 0, phase = 0, g = 0;
             int win = 0, win_phase = 0;  // accumulator window ring
@@ -584,20 +648,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
                     const bool new_window = C::kPromote ? true : (kb == 0);
                     if (new_window) {
-                        if (!mbar_wait(&tmem_empty[win], win_phase ^ 1, abort_flag, limit)) {
+                        if (!mbar_wait(&tmem_empty[win], win_phase ^ 1, abort_flag, limit, note, wait_id(3, tile, kb, win))) {
                             ok = false;
                             break;
                         }
                         tc_fence_after();
                     }
-                    if (!mbar_wait(&full[stage], phase, abort_flag, limit)) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag, limit, note, wait_id(4, tile, kb, stage))) {
+                        if (note != nullptr) atomicCAS(note + 1, 0ull, ((unsigned long long)s_prod_state[0] << 32) | (unsigned)s_prod_state[1]);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + (size_t)stage * C::kStageBytes);
                     const uint32_t sb = sa + kATileBytes;
-                    const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
+                    const uint64_t adesc = p.a_mn ? make_smem_desc_mn(sa) : make_smem_desc(sa);
+                    const uint64_t bdesc = p.b_mn ? make_smem_desc_mn(sb) : make_smem_desc(sb);
                     const uint32_t tmem_d = tmem_base + (uint32_t)(win * kBlockN);
                     if constexpr (kMx) {
                         // scale atoms of this stage -> TMEM (alternating column sets), then four K=32 MMAs that read them
@@ -616,10 +682,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 4; ++j) {
                             // +32 bytes along K inside the swizzle atom = +2 in the 16-byte start-address field
                             if constexpr (kPair)
-                                umma_pair<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                umma_pair<kFp8>(tmem_d, adesc + (uint64_t)j * a_kstep, bdesc + (uint64_t)j * b_kstep, idesc,
                                                 (new_window && j == 0) ? 0u : 1u);
                             else
-                                umma<kFp8>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc,
+                                umma<kFp8>(tmem_d, adesc + (uint64_t)j * a_kstep, bdesc + (uint64_t)j * b_kstep, idesc,
                                            (new_window && j == 0) ? 0u : 1u);
                         }
                     }
@@ -699,7 +765,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const bool warp_has_rows = ti.c_row + q * 32 < ti.c_row_end;
                 for (int kb = 0; kb < ti.num_kb; ++kb) {
                     if (!warp_has_rows) {
-                        if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
+                        if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit, note, wait_id(7, tile, kb, warp))) {
                             ok = false;
                             break;
                         }
@@ -711,9 +777,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         continue;
                     }
-                    const float sa = __ldg(sa_row + kb);
+                    const float sa = __ldcg(sa_row + kb);  // L2 only: with arrival gating these scales were written by other GPUs during this kernel
                     const float s_lo = sa * __ldg(sb0 + kb), s_hi = kSwiGLU ? sa * __ldg(sb1 + kb) : s_lo;
-                    if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
+                    if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit, note, wait_id(5, tile, kb, warp))) {
                         ok = false;
                         break;
                     }
@@ -760,7 +826,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             } else {
-                if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit)) {
+                if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit, note, wait_id(6, tile, 0, warp))) {
                     ok = false;
                     break;
                 }
@@ -892,6 +958,20 @@ bool make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64
     return r == CUDA_SUCCESS;
 }
 
+// 2-D row-major [k_rows, mn_cols] bf16 tensor whose contiguous dimension is the operand's row index (MN-major operand):
+// box = 64 columns (128 bytes) x 64 rows, 128B swizzle.
+bool make_map_mn(CUtensorMap* map, const void* ptr, uint64_t k_rows, uint64_t mn_cols) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {mn_cols, k_rows};
+    cuuint64_t strides[1] = {mn_cols * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
 cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
     using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
@@ -900,10 +980,13 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
     bool ok;
     if (a.mode == 0) {
         ok = make_map(&map_a, a.a, kFp8, (uint64_t)a.m_total, (uint64_t)a.k, kBlockM) &&
-             make_map(&map_b, a.b, kFp8, (uint64_t)a.num_groups * a.n, (uint64_t)a.k, b_box_rows);
+             (a.b_mn ? make_map_mn(&map_b, a.b, (uint64_t)a.num_groups * a.k, (uint64_t)a.n)  // B given as [G, K, N]
+                     : make_map(&map_b, a.b, kFp8, (uint64_t)a.num_groups * a.n, (uint64_t)a.k, b_box_rows));
     } else {
-        ok = make_map(&map_a, a.a, kFp8, (uint64_t)a.n, (uint64_t)a.m_total, kBlockM) &&
-             make_map(&map_b, a.b, kFp8, (uint64_t)a.k, (uint64_t)a.m_total, b_box_rows);
+        ok = (a.a_mn ? make_map_mn(&map_a, a.a, (uint64_t)a.m_total, (uint64_t)a.n)   // A given as [M, N_out]
+                     : make_map(&map_a, a.a, kFp8, (uint64_t)a.n, (uint64_t)a.m_total, kBlockM)) &&
+             (a.b_mn ? make_map_mn(&map_b, a.b, (uint64_t)a.m_total, (uint64_t)a.k)   // B given as [M, K_out]
+                     : make_map(&map_b, a.b, kFp8, (uint64_t)a.k, (uint64_t)a.m_total, b_box_rows));
     }
     if (!ok) return cudaErrorInvalidValue;
     auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
@@ -947,6 +1030,10 @@ cudaError_t launch_sel(const GroupedGemmArgs& a, cudaStream_t stream) {
 
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
     if (a.num_groups < 1 || a.num_groups > kMaxGroups || a.num_sms < 1) return cudaErrorInvalidValue;
+    // MN-major operands: bf16, no swiglu, single CTAs; mode 0 takes B that way (input gradients read the weight in place),
+    // mode 1 takes both (weight gradients read the output gradient and the activation in place)
+    if ((a.a_mn || a.b_mn) && (a.fp8 || a.swiglu || a.cta_pairs || (a.mode == 0 && a.a_mn) || (a.mode == 1 && !(a.a_mn && a.b_mn)) || a.n % 64 != 0))
+        return cudaErrorInvalidValue;
     if (a.m_total <= 0) return cudaSuccess;
     const int kb = a.fp8 ? 128 : 64;
     if (a.mode == 0) {

@@ -95,7 +95,11 @@ class _GroupedLinear(torch.autograd.Function):
     def backward(ctx, grad):
         x, w, m_offsets = ctx.saved_tensors
         grad = grad.contiguous()
-        if x.is_cuda:
+        if x.is_cuda and x.size(1) % 128 == 0 and w.size(1) % 128 == 0:
+            # weight, gradient and activation are read in place as MN-major operands: no transposed copies
+            dx = gg.grouped_gemm_dgrad(grad, w, m_offsets)
+            dw = gg.grouped_gemm_wgrad_inplace(grad, x, m_offsets)
+        elif x.is_cuda:
             dx = gg.grouped_gemm(grad, gg.transpose_last2(w), m_offsets)
             dw = gg.grouped_gemm_wgrad(gg.transpose_last2(grad), gg.transpose_last2(x), m_offsets)
         else:
@@ -298,6 +302,13 @@ class MoELayer(nn.Module):
 # fused forward: expert-major dispatch -> arrival-gated GEMM1 -> cast -> GEMM2 with scatter epilogue -> local reduce
 # ---------------------------------------------------------------------------------------------------------
 UNIT_ROWS = 8  # rows of one expert a dispatch warp sends between two arrival-counter updates
+# SMs the arrival-gated GEMM leaves to the dispatch kernel when the two overlap. The dispatch CTAs are small enough to share an
+# SM with a GEMM CTA of the natively block-scaled kernel (6 warps), but not with one of the promotion kernel (10 warps of 160
+# registers: three such warps fill a scheduler partition's quarter of the register file). A GEMM that got all SMs before the
+# dispatch CTAs were placed would then wait for rows that nobody can send, so some SMs are never given to it.
+RESERVED_SMS_NATIVE = 4
+RESERVED_SMS_PROMOTE = 12
+GEMM_TIMEOUT_MS = 2000.0  # bound of every wait inside the gated GEMMs (pipeline barriers and arrival counters)
 
 
 class _FusedWorkspace:
@@ -325,7 +336,7 @@ class _FusedWorkspace:
         self.my_counts = torch.zeros(E, **i32)
         self.sel_list = torch.zeros(E * T, **i32)
         self.send_base = torch.zeros(E, **i32)
-        self.unit_start = torch.zeros(E + 1, **i32)
+        self.unit_start = torch.zeros(E + 2, **i32)  # prefix of work units [E + 1] and the hand-out counter
         self.m_offsets = torch.zeros(L + 1, **i32)
         self.m_ends = torch.zeros(L, **i32)
         self.peer_bases = torch.zeros(4 * R, dtype=torch.int64, device=dev)
@@ -340,12 +351,13 @@ class _FusedWorkspace:
 
     def enable_trace(self) -> None:
         """[dispatch first start, dispatch last end, GEMM1 first tile load, GEMM1 last epilogue end] in ns of the GPU's
-        global timer (min / max over the CTAs), for the overlap evidence."""
-        self.trace = torch.zeros(4, dtype=torch.int64, device=self.h.device)
+        global timer (min / max over the CTAs), for the overlap evidence; [4] = the first bounded wait of GEMM1 that gave up
+        (role, tile, K block, slot), [5] = what GEMM1's loader was doing then."""
+        self.trace = torch.zeros(6, dtype=torch.int64, device=self.h.device)
 
     def reset_trace(self) -> None:
         big = torch.iinfo(torch.int64).max
-        self.trace.copy_(torch.tensor([big, 0, big, 0], dtype=torch.int64))
+        self.trace.copy_(torch.tensor([big, 0, big, 0, 0, 0], dtype=torch.int64))
 
 
 def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_sms: int = 0):
@@ -389,17 +401,18 @@ def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_
     for l, w in zip(layers, wss):
         (w13, s13), (w2, s2) = l._fp8
         R_, L = l.buffer.group_size, l.num_local_experts
-        gate = dict(ready=w.arrived, expected=w.expected, trace=None if w.trace is None else w.trace[2:4])
+        gate = dict(ready=w.arrived, expected=w.expected, trace=None if w.trace is None else w.trace[2:6])
+        sms1 = (148 - (RESERVED_SMS_NATIVE if native else RESERVED_SMS_PROMOTE)) if comm is not cur else 0
         if native:
             wide = R_ * w.num_tokens * K >= 512 * E
-            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, w.h, 0, 2000.0, w.m_ends, w.recv_scales, l._mx[0 if wide else 2], **gate)
+            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, w.h, sms1, GEMM_TIMEOUT_MS, w.m_ends, w.recv_scales, l._mx[0 if wide else 2], **gate)
             C.per_token_cast_to_fp8(w.h, True, False, None, 1, w.hq, w.hs, w.m_offsets[L:], True)
-            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, 2000.0, w.m_ends, w.hs, l._mx[1],
+            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, GEMM_TIMEOUT_MS, w.m_ends, w.hs, l._mx[1],
                            row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
         else:
-            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, w.recv_scales, s13, w.h, 0, 2000.0, w.m_ends, None, None, **gate)
+            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, w.recv_scales, s13, w.h, sms1, GEMM_TIMEOUT_MS, w.m_ends, None, None, **gate)
             C.per_token_cast_to_fp8(w.h, False, False, None, 1, w.hq, w.hs, w.m_offsets[L:], False)
-            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, w.hs, s2, None, 0, 2000.0, w.m_ends, None, None,
+            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, w.hs, s2, None, 0, GEMM_TIMEOUT_MS, w.m_ends, None, None,
                            row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
     # every rank's second GEMM has finished scattering before anybody sums its stage
     C.barrier(rts)

@@ -58,6 +58,18 @@ def grouped_gemm_wgrad(a_t: torch.Tensor, b_t: torch.Tensor, m_offsets: torch.Te
     return _ext.load().grouped_gemm(a_t, b_t, m_offsets, 1, False, None, None, out, num_sms)
 
 
+def grouped_gemm_dgrad(grad: torch.Tensor, w: torch.Tensor, m_offsets: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Input gradient of ``y = grouped_gemm(x, w)``: ``dx[m] = grad[m] @ w[g]`` for the rows of expert g, with ``w``
+    ``[G, N, K]`` read in place as an MN-major operand (no transposed copy of the weight). bf16; ``grad`` is ``[M, N]``."""
+    return _ext.load().grouped_gemm(grad, w, m_offsets, 0, False, None, None, out, 0, 2000.0, mn_major=True)
+
+
+def grouped_gemm_wgrad_inplace(grad: torch.Tensor, x: torch.Tensor, m_offsets: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Weight gradient ``dw[g] = grad[rows of g].T @ x[rows of g]`` with ``grad`` ``[M, N_out]`` and ``x`` ``[M, K_out]`` read in
+    place as MN-major operands (no transposed copies). Group boundaries on multiples of 64 rows. Returns bf16 ``[G, N_out, K_out]``."""
+    return _ext.load().grouped_gemm(grad, x, m_offsets, 1, False, None, None, out, 0, 2000.0, mn_major=True)
+
+
 def reference_grouped_gemm(a: torch.Tensor, b: torch.Tensor, m_offsets: torch.Tensor, swiglu: bool = False,
                            a_scales: Optional[torch.Tensor] = None, b_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Plain PyTorch fp32 reference of :func:`grouped_gemm` (used by the tests)."""

@@ -193,3 +193,49 @@ def test_fp8_native_block_scaling(swiglu, wide):
     assert C.gemm_error(0) == 0
     ref = reference_grouped_gemm(a, b, offs, swiglu=swiglu, a_scales=a_s, b_scales=b_s)
     assert _rel_err(c, ref) < (1.5e-2 if swiglu else 1e-2), _rel_err(c, ref)
+
+
+@pytest.mark.parametrize("rows,N_w,K_w", [([128, 256, 0, 384], 256, 512), ([40, 200, 77], 384, 128), ([256] * 3, 1408, 4096)])
+def test_bf16_dgrad_reads_weight_in_place(rows, N_w, K_w):
+    """dx = grad @ w[g] with the forward weight [G, N, K] consumed as an MN-major operand: no transposed copy."""
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm_dgrad
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(11)
+    G, M = len(rows), sum(rows)
+    grad = torch.randn(M, N_w, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(G, N_w, K_w, device="cuda") * 0.1).to(torch.bfloat16)
+    offs = _offsets(rows)
+    dx = grouped_gemm_dgrad(grad, w, offs)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0 and dx.shape == (M, K_w)
+    o = offs.tolist()
+    for g in range(G):
+        if rows[g]:
+            ref = grad[o[g]:o[g + 1]].float() @ w[g].float()
+            assert _rel_err(dx[o[g]:o[g + 1]], ref) < 1e-2, (g, _rel_err(dx[o[g]:o[g + 1]], ref))
+
+
+@pytest.mark.parametrize("rows,n_out,k_out", [([128, 0, 256], 256, 128), ([64, 192, 128], 384, 256), ([512, 256], 1408, 4096)])
+def test_bf16_wgrad_reads_gradient_and_activation_in_place(rows, n_out, k_out):
+    """dw[g] = grad[rows of g].T @ x[rows of g] with both operands MN-major: no transposed copies."""
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import grouped_gemm_wgrad_inplace
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(12)
+    M = sum(rows)
+    dy = torch.randn(M, n_out, device="cuda").to(torch.bfloat16)
+    x = torch.randn(M, k_out, device="cuda").to(torch.bfloat16)
+    offs = _offsets(rows)
+    dw = grouped_gemm_wgrad_inplace(dy, x, offs)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0 and dw.shape == (len(rows), n_out, k_out)
+    o = offs.tolist()
+    for g in range(len(rows)):
+        ref = dy[o[g]:o[g + 1]].float().t() @ x[o[g]:o[g + 1]].float()
+        if rows[g] == 0:
+            assert dw[g].float().abs().max().item() == 0
+        else:
+            assert _rel_err(dw[g], ref) < 1e-2, (g, _rel_err(dw[g], ref))

@@ -259,6 +259,33 @@ def spread_us(samples_ms):
             "min": round(max_over_ranks(min(samples_ms) * 1e3), 3)}
 
 
+def nccl_all_to_all_floor(rank: int, world: int, topk_idx: torch.Tensor, bytes_per_selection: int, steps: int, flush: torch.Tensor,
+                          per_rank_once: bool = False):
+    """Time of one plain ``dist.all_to_all_single`` (NCCL over NVLink) that moves the byte volume of a dispatch or combine
+    with this routing: per destination rank, ``bytes_per_selection`` for every (token, expert) selection that lives there
+    (``per_rank_once``: for every token that has at least one expert there). This is the collective the reference's
+    single-node low-latency path is built on (deep_ep/buffer.py:2297, 2735); no packing, casting or reduction is included."""
+    L = NUM_EXPERTS // world
+    dest = torch.where(topk_idx >= 0, topk_idx // L, torch.full_like(topk_idx, -1))
+    if per_rank_once:
+        counts = torch.stack([(dest == r).any(dim=1).sum() for r in range(world)])
+    else:
+        counts = torch.stack([(dest == r).sum() for r in range(world)])
+    send_counts = (counts * bytes_per_selection).to(torch.int64)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts)
+    send_split, recv_split = send_counts.tolist(), recv_counts.tolist()
+    send = torch.empty(max(sum(send_split), 1), dtype=torch.uint8, device="cuda")
+    recv = torch.empty(max(sum(recv_split), 1), dtype=torch.uint8, device="cuda")
+
+    def fn():
+        dist.all_to_all_single(recv, send, recv_split, send_split)
+
+    for _ in range(3):
+        fn()
+    return max_over_ranks(timed_loop(fn, steps, flush) * 1e3)
+
+
 def make_inputs(rank: int, tokens: int, masked_fraction: float = 0.0):
     g = torch.Generator(device="cpu").manual_seed(rank)
     x = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16)
@@ -366,6 +393,17 @@ def run_ours(args):
         disp_us = max_over_ranks(sum(a.elapsed_time(b) for a, b in d_ev) / sub_steps * 1e3)
         comb_us = max_over_ranks(sum(a.elapsed_time(b) for a, b in c_ev) / sub_steps * 1e3)
 
+    # ---------------- plain NCCL all-to-all of the same byte volumes (what a library call alone costs) ----------------
+    nccl_floor = None
+    if not args.skip_breakdown:
+        try:
+            d_us = nccl_all_to_all_floor(rank, world, topk_idx, HIDDEN + HIDDEN // 128 * 4 + 16, sub_steps, flush)
+            c_us = nccl_all_to_all_floor(rank, world, topk_idx, HIDDEN * 2, sub_steps, flush)
+            nccl_floor = {"ll_dispatch_bytes_us": round(d_us, 2), "ll_combine_bytes_us": round(c_us, 2), "sum_us": round(d_us + c_us, 2),
+                          "what": "dist.all_to_all_single of the per-destination byte volumes only (no cast, pack, count exchange or reduce)"}
+        except Exception as e:  # pragma: no cover
+            nccl_floor = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+
     # ---------------- end to end: pinned host inputs in, result out, every step ----------------
     # The step's inputs (activations, expert ids, weights) sit packed in ONE pinned host buffer and cross PCIe as one
     # host-to-device copy; the combine kernel writes the step's result straight into pinned host memory (its stores are the
@@ -386,17 +424,30 @@ def run_ours(args):
         _, _, h, _, _ = buf.low_latency_dispatch(x_d, idx_d, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
         buf.low_latency_combine(sim_gemm_out, idx_d, w_d, h, out=out_p)
 
+    def e2e_step_copy_out():
+        # the same step with the result produced in device memory and copied out by the copy engine
+        stage_d.copy_(stage_p, non_blocking=True)
+        _, _, h, _, _ = buf.low_latency_dispatch(x_d, idx_d, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+        buf.low_latency_combine(sim_gemm_out, idx_d, w_d, h, out=out)
+        out_p.copy_(out, non_blocking=True)
+
     # the host copy of the result must equal what the device path produces
     out_p.zero_()
     e2e_step()
     ll_step()
     torch.cuda.synchronize()
     assert torch.equal(out_p, out.cpu()), "end-to-end result in pinned host memory differs from the device result"
-    for _ in range(warmup):
-        e2e_step()
-    e2e_samples = timed_samples(e2e_step, steps, flush)
-    e2e_us = max_over_ranks(sum(e2e_samples) / steps * 1e3)
-    e2e_spread = spread_us(e2e_samples)
+    # Which of the two ways of getting the result to the host is faster depends on the machine (where the pinned pages sit
+    # relative to the GPU's PCIe root); both are timed with the full protocol and the faster one is the reported value.
+    e2e_variants = {}
+    for name, fn in (("result_stored_to_pinned_host_by_kernel", e2e_step), ("result_copied_out_by_copy_engine", e2e_step_copy_out)):
+        for _ in range(warmup):
+            fn()
+        smp = timed_samples(fn, steps, flush)
+        e2e_variants[name] = {"value": round(max_over_ranks(sum(smp) / steps * 1e3), 3), **spread_us(smp)}
+    e2e_how = min(e2e_variants, key=lambda k: e2e_variants[k]["value"])
+    e2e_us = e2e_variants[e2e_how]["value"]
+    e2e_spread = {"median": e2e_variants[e2e_how]["median"], "min": e2e_variants[e2e_how]["min"]}
     h2d = stage_p.numel()
     d2h = out_p.numel() * 2
     buf.check_status(sync=True)
@@ -451,8 +502,8 @@ def run_ours(args):
                    "samples": clocks["samples"]},
         "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "median": e2e_spread["median"], "min": e2e_spread["min"],
-                "how": "one packed pinned buffer (x|topk_idx|topk_weights) -> one H2D copy; the combine kernel stores the result "
-                       "into pinned host memory"},
+                "how": "one packed pinned buffer (x|topk_idx|topk_weights) -> one H2D copy; " + e2e_how.replace("_", " "),
+                "variants": e2e_variants},
         "value_median": ll_spread["median"],
         "value_min": ll_spread["min"],
         "ll_zero_copy_us": zc_us,
@@ -461,6 +512,7 @@ def run_ours(args):
         "ll_dispatch_us": None if disp_us is None else round(disp_us, 2),
         "ll_combine_us": None if comb_us is None else round(comb_us, 2),
         "ll_masked_us": masked,
+        "nccl_all_to_all_floor": nccl_floor,
         "normal": normal,
         "impl": "deepep_efa_b200",
     }
@@ -540,6 +592,14 @@ def bench_normal(buf, rank, world, flush, steps, warmup):
         ms = max_over_ranks(timed_loop(fn, steps, flush))
         nbytes = n_recv * HIDDEN * 2 * ((1 + 4 / 128) / 2 if name.startswith("dispatch") else 1)
         res[name] = {"ms": round(ms, 4), "GBps": round(nbytes / 1e9 / (ms / 1e3), 1)}
+    try:
+        d_us = nccl_all_to_all_floor(rank, world, topk_idx, int(HIDDEN * (1 + 4 / 128)), steps, flush, per_rank_once=True)
+        c_us = nccl_all_to_all_floor(rank, world, topk_idx, HIDDEN * 2, steps, flush, per_rank_once=True)
+        res["nccl_all_to_all_floor"] = {"dispatch_fp8_ms": round(d_us / 1e3, 4), "dispatch_fp8_GBps": round(n_recv * HIDDEN * 2 * (1 + 4 / 128) / 2 / 1e9 / (d_us / 1e6), 1),
+                                        "combine_bf16_ms": round(c_us / 1e3, 4), "combine_bf16_GBps": round(n_recv * HIDDEN * 2 / 1e9 / (c_us / 1e6), 1),
+                                        "what": "dist.all_to_all_single of the same rows, one per (token, destination rank); GB/s with the same byte definition"}
+    except Exception as e:  # pragma: no cover
+        res["nccl_all_to_all_floor"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
     res["default_num_sms"] = {"dispatch": ep.Buffer.get_dispatch_config(world).num_sms, "combine": ep.Buffer.get_combine_config(world).num_sms}
     res["checked"] = "constant-per-source payload arrives as one segment per source; combine(dispatch(x)) == x * hits"
     buf.check_status(sync=True)

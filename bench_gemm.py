@@ -1,6 +1,11 @@
 """Grouped expert GEMM micro-benchmark (one GPU): the tcgen05 kernel of this library against a per-expert cuBLAS loop.
 
     python bench_gemm.py [--experts 8] [--rows 4096] [--k 7168] [--n 4096] [--dtype bf16|fp8] [--swiglu] [--iters 20]
+                         [--op fwd|dgrad|wgrad|wgrad_t]
+
+``--op`` (bf16): ``fwd`` y = x @ w[g].T; ``dgrad`` dx = dy @ w[g] with the weight read in place (MN-major operand);
+``wgrad`` dw[g] = dy.T @ x with both operands read in place; ``wgrad_t`` the same product from transposed copies (the
+K-major form), the transposes not timed.
 
 Prints one JSON line per run with achieved TFLOP/s and the fraction of the measured cuBLAS BF16 peak
 (MEASURED_PEAKS.json, "of measured"). ``--rows`` is the number of rows per expert (multiple of 128). Inputs exceed L2
@@ -30,6 +35,7 @@ def main():
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--op", default="fwd", choices=["fwd", "dgrad", "wgrad", "wgrad_t"])
     ap.add_argument("--native-scaling", action="store_true",
                     help="fp8 only: power-of-two scales applied by the tensor core (UE8M0 block scaling) instead of per-K-block promotion")
     args = ap.parse_args()
@@ -57,10 +63,20 @@ def main():
             fn = lambda: grouped_gemm(a, b, offs, swiglu=args.swiglu, sfa_atoms=build_sf_atoms_a(a_s), sfb_atoms=atoms_b)
         else:
             fn = lambda: grouped_gemm(a, b, offs, swiglu=args.swiglu, a_scales=a_s, b_scales=b_s)
-    else:
+    elif args.op == "fwd":
         fn = lambda: grouped_gemm(x, w, offs, swiglu=args.swiglu)
+    else:
+        from deepep_efa_b200.ops.grouped_gemm import grouped_gemm_dgrad, grouped_gemm_wgrad, grouped_gemm_wgrad_inplace
+        dy = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+        if args.op == "dgrad":
+            fn = lambda: grouped_gemm_dgrad(dy, w, offs)
+        elif args.op == "wgrad":
+            fn = lambda: grouped_gemm_wgrad_inplace(dy, x, offs)
+        else:
+            dy_t, x_t = dy.t().contiguous(), x.t().contiguous()
+            fn = lambda: grouped_gemm_wgrad(dy_t, x_t, offs)
 
-    from bench import ramp_clocks
+    from bench import ClockSampler, ramp_clocks
     ramp_clocks(0)
 
     def timeit(f):
@@ -79,7 +95,10 @@ def main():
         torch.cuda.synchronize()
         return s.elapsed_time(e) / args.iters
 
+    sampler = ClockSampler(gpus={0})
+    sampler.start()
     ms = timeit(fn)
+    clocks = sampler.stop({0})
     assert C.gemm_error(0) == 0
     flops = 2.0 * M * N * K
     peaks = {}
@@ -88,9 +107,11 @@ def main():
     except Exception:
         pass
     peak = peaks.get("bf16_tflops", 1590.0)
-    out = {"kernel": "grouped_gemm", "dtype": args.dtype, "native_scaling": bool(args.native_scaling), "swiglu": args.swiglu, "experts": G, "rows_per_expert": R, "k": K, "n": N,
-           "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_cublas_peak": round(flops / ms / 1e9 / peak, 3)}
-    if not args.no_cublas and args.dtype == "bf16" and not args.swiglu:
+    out = {"kernel": "grouped_gemm", "op": args.op, "dtype": args.dtype, "native_scaling": bool(args.native_scaling), "swiglu": args.swiglu, "experts": G, "rows_per_expert": R, "k": K, "n": N,
+           "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_cublas_peak": round(flops / ms / 1e9 / peak, 3),
+           "sm_mhz_median": clocks["sm_mhz"], "throttle_reasons": clocks["reasons"],
+           "ms_x_mhz": None if clocks["sm_mhz"] is None else round(ms * clocks["sm_mhz"], 1)}
+    if not args.no_cublas and args.dtype == "bf16" and not args.swiglu and args.op == "fwd":
         def loop():
             for g in range(G):
                 torch.matmul(x[g * R:(g + 1) * R], w[g].t())

@@ -1,5 +1,7 @@
-"""Micro-benchmark of the memory-bound helper kernels (one GPU): layout, standalone FP8 cast, expert-major plan / gathers,
-two-level bookkeeping, and the training-step elementwise kernels.
+"""Micro-benchmark of the memory-bound helper kernels (one GPU): layout, standalone FP8 cast (plain, masked, scale atoms),
+scale-atom builders, expert-major plan / gathers, two-level bookkeeping, the training-step elementwise kernels, and the
+single-rank forms of the collective kernels of the fused MoE path (count exchange, expert-major dispatch, stage reduce,
+barrier).
 
     python bench_kernels.py [--rows 32768] [--hidden 7168] [--iters 20] [--warmup 5] [--only NAME]
 
@@ -55,7 +57,49 @@ def main():
     ids, cnts, prefix, pos = Hh.routing_sort(member, 8)
     S = int(prefix[-1].item())
 
+    # fused-path kernels on one rank: a layer with a tiny FFN gives the workspace (rows, scales, stage) at full hidden size
+    from deepep_efa_b200.models.moe import UNIT_ROWS, MoEConfig, MoELayer
+    from deepep_efa_b200.ops.grouped_gemm import build_sf_atoms_a, build_sf_atoms_b
+    from deepep_efa_b200.parallel.virtual import VirtualCluster
+    Tf = min(M, 4096)
+    rows_f = (Tf * K + E * 127 + 127) // 128 * 128
+    vc = VirtualCluster(1, num_nvl_bytes=(64 << 20) + 2 * (rows_f * (H + H // 128 * 4 + 4) + Tf * K * H * 2))
+    fbuf = vc.buffers[0]
+    layer = MoELayer(MoEConfig(hidden=H, intermediate=128, num_experts=E, num_topk=K), fbuf)
+    fw = layer.fused_workspace(Tf)
+    rts = [fbuf.runtime]
+    xf, idxf, wf = x[:Tf].contiguous(), topk[:Tf].contiguous(), w[:Tf].contiguous()
+    notify_args = [(idxf, fw.recv_x, fw.recv_scales_raw, fw.recv_info, fw.stage, fw.my_counts, fw.sel_list, fw.send_base, fw.unit_start,
+                    fw.m_offsets, fw.m_ends, fw.peer_bases)]
+    disp_args = [(xf, fw.my_counts, fw.sel_list, fw.send_base, fw.unit_start, fw.peer_bases, None, None)]
+
+    def em_dispatch():
+        C.em_notify(rts, notify_args, E, UNIT_ROWS)
+        C.em_dispatch(rts, disp_args, E, K, UNIT_ROWS, False, False, 148)
+
+    out_f = torch.empty(Tf, H, dtype=torch.bfloat16, device="cuda")
+    xs_q, xs_s = C.per_token_cast_to_fp8(x, True, False)
+    b_s = torch.exp2(torch.randint(-8, 0, (E // R, 4096 // 128, H // 128), device="cuda").float())
+    cnts = torch.randint(0, 129, (M // 128,), device="cuda", dtype=torch.int32)
+    nrows = torch.tensor([M // 2], dtype=torch.int32, device="cuda")
+    recv_prefix = torch.arange(0, M + 1, M // 8, dtype=torch.int32, device="cuda")
+    in_local = torch.rand(M, 4, device="cuda", generator=g) < 0.5
+    seg_n = 64
+    seg = torch.tensor([[i * (M // seg_n) * H * 2, ((i * 7) % seg_n) * (M // seg_n) * H * 2, (M // seg_n) * H * 2] for i in range(seg_n)],
+                       dtype=torch.int64, device="cuda")
+    dst_rows = torch.empty_like(x)
+
     cases = {
+        "em_notify_kernel": (lambda: C.em_notify(rts, notify_args, E, UNIT_ROWS), Tf * K * 8 + E * Tf * 4 // 8),
+        "em_dispatch_kernel": (em_dispatch, Tf * K * (H * 2 + H + H // 128 * 4 + 4)),
+        "stage_reduce_kernel": (lambda: C.stage_reduce(fw.stage, out_f, idxf, wf, E), Tf * K * H * 2 + Tf * H * 2),
+        "barrier_kernel": (lambda: C.barrier(rts), 64),
+        "sfa_atoms_kernel": (lambda: build_sf_atoms_a(xs_s), 2 * M * (H // 128) * 4),
+        "sfb_atoms_kernel": (lambda: build_sf_atoms_b(b_s, 4096, True, True), 2 * b_s.numel() * 4),
+        "fp8_cast_kernel_masked": (lambda: C.per_token_cast_to_fp8(x, False, False, cnts, 128), int(cnts.sum()) * H * 3),
+        "fp8_cast_kernel_atoms_devcount": (lambda: C.per_token_cast_to_fp8(x, True, False, None, 1, None, None, nrows, True), M // 2 * H * 3),
+        "recv_src_meta_kernel": (lambda: Hh.recv_src_meta(recv_prefix, in_local, M), M * 4 + M * 8),
+        "segmented_copy_kernel": (lambda: Hh.segmented_copy(x, dst_rows, seg), 2 * M * H * 2),
         "layout_kernel": (lambda: Hh.layout_hier(topk, E, R, R), M * K * 8 + M * R),
         "fp8_cast_kernel": (lambda: C.per_token_cast_to_fp8(x, False, False), M * H * 3 + M * H // 128 * 4),
         "build_plan_kernel": (lambda: build_expert_plan(local, counts), M * K * 12 + plan.num_rows * 8),

@@ -63,7 +63,8 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
                            c10::optional<torch::Tensor> sfa_atoms, c10::optional<torch::Tensor> sfb_atoms,
                            c10::optional<torch::Tensor> ready, c10::optional<torch::Tensor> expected,
                            c10::optional<torch::Tensor> row_info, c10::optional<torch::Tensor> scatter_bases,
-                           c10::optional<torch::Tensor> trace, bool mn_major) {
+                           c10::optional<torch::Tensor> trace, bool mn_major, c10::optional<torch::Tensor> out_fp8,
+                           c10::optional<torch::Tensor> out_atoms) {
     DXG_CHECK(a.is_cuda() && b.is_cuda() && m_offsets.is_cuda(), "operands must be CUDA tensors");
     DXG_CHECK(a.is_contiguous() && b.is_contiguous() && m_offsets.is_contiguous(), "operands must be contiguous");
     DXG_CHECK(m_offsets.scalar_type() == torch::kInt32 && m_offsets.dim() == 1 && m_offsets.numel() >= 2, "m_offsets must be int32 [G+1]");
@@ -100,8 +101,8 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         DXG_CHECK(!swiglu || N % 2 == 0, "swiglu needs an even N (gate and up stacked)");
         const int64_t out_cols = swiglu ? N / 2 : N;
         // with the scatter epilogue nothing is stored to `c`: every row goes to the address its row_info word names
-        c = out.has_value() ? *out : torch::empty({row_info.has_value() ? (int64_t)0 : M, out_cols}, bf16);
-        DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && (row_info.has_value() || c.numel() == M * out_cols), "out must be contiguous bf16 [M, N]");
+        c = out.has_value() ? *out : torch::empty({(row_info.has_value() || out_fp8.has_value()) ? (int64_t)0 : M, out_cols}, bf16);
+        DXG_CHECK(c.scalar_type() == torch::kBFloat16 && c.is_contiguous() && (row_info.has_value() || out_fp8.has_value() || c.numel() == M * out_cols), "out must be contiguous bf16 [M, N]");
         p.m_total = (int)M;
         p.n = (int)N;
         p.k = (int)K;
@@ -172,6 +173,16 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         DXG_CHECK(scatter_bases->element_size() == 8 && scatter_bases->is_contiguous() && scatter_bases->numel() >= 1, "scatter_bases must be 64-bit pointers");
         p.row_info = row_info->data_ptr<int>();
         p.scatter_bases = reinterpret_cast<const unsigned long long*>(scatter_bases->data_ptr());
+    }
+    if (out_fp8.has_value() || out_atoms.has_value()) {
+        DXG_CHECK(out_fp8.has_value() && out_atoms.has_value() && same_dev(out_fp8) && same_dev(out_atoms), "out_fp8 and out_atoms go together, on A's device");
+        DXG_CHECK(mode == 0 && swiglu && p.sfa_atoms != nullptr && p.mx_wide == 1, "quantised output needs the natively block-scaled kernel with wide SwiGLU tiles");
+        const int64_t inter = p.n / 2;
+        DXG_CHECK(out_fp8->element_size() == 1 && out_fp8->is_contiguous() && out_fp8->numel() == (int64_t)p.m_total * inter, "out_fp8 must be e4m3 [M, N/2]");
+        DXG_CHECK(out_atoms->element_size() == 1 && out_atoms->is_contiguous() && out_atoms->numel() >= (((int64_t)p.m_total + 127) / 128) * (inter / 128) * 512,
+                  "out_atoms must be uint8 [ceil(M/128), N/2/128, 512]");
+        p.c_fp8 = reinterpret_cast<uint8_t*>(out_fp8->data_ptr());
+        p.c_atoms = reinterpret_cast<uint8_t*>(out_atoms->data_ptr());
     }
     if (trace.has_value()) {
         DXG_CHECK(trace->element_size() == 8 && trace->is_contiguous() && trace->numel() >= 4, "trace must be 64-bit [4]");
@@ -334,7 +345,8 @@ void bind_gemm(py::module_& m) {
           py::arg("a_scales") = py::none(), py::arg("b_scales") = py::none(), py::arg("out") = py::none(), py::arg("num_sms") = 0,
           py::arg("timeout_ms") = 2000.0, py::arg("m_ends") = py::none(), py::arg("sfa_atoms") = py::none(), py::arg("sfb_atoms") = py::none(),
           py::arg("ready") = py::none(), py::arg("expected") = py::none(), py::arg("row_info") = py::none(),
-          py::arg("scatter_bases") = py::none(), py::arg("trace") = py::none(), py::arg("mn_major") = false);
+          py::arg("scatter_bases") = py::none(), py::arg("trace") = py::none(), py::arg("mn_major") = false,
+          py::arg("out_fp8") = py::none(), py::arg("out_atoms") = py::none());
     m.def("build_plan", &build_plan);
     m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(), py::arg("out") = py::none());
     m.def("gather_reduce_rows", &gather_reduce_rows, py::arg("src"), py::arg("pos"), py::arg("w") = py::none(), py::arg("out") = py::none());

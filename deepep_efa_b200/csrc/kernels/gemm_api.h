@@ -65,6 +65,11 @@ struct GroupedGemmArgs {
     // the forward weight as it is). mode 1: a_mn = b_mn = 1, A given as [M_total, N_out], B as [M_total, K_out] (weight
     // gradients: output gradient and activation as they are).
     int a_mn, b_mn;
+    // Quantised output (natively block-scaled kernel with 256-column SwiGLU tiles only): instead of bf16 rows in `c`, write
+    // e4m3 rows [M_total, N/2] to c_fp8 and their power-of-two scales as UE8M0 scale atoms [ceil(M/128)][N/2/128][512] to
+    // c_atoms: the activation operand of the next natively block-scaled GEMM, without a cast pass in between.
+    uint8_t* c_fp8;
+    uint8_t* c_atoms;
 };
 
 // Returns cudaErrorInvalidValue for unsupported shapes (divisibility rules are in grouped_gemm.cu).

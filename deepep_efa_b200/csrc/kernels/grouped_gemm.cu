@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 
 #include "gemm_api.h"
+#include "prims.cuh"
 
 namespace dx {
 
@@ -855,6 +856,54 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) release_window(&tmem_empty[win]);
+                    if constexpr (kMx && C::kOutCols == 128) {
+                        if (p.c_fp8 != nullptr) {
+                            // The tile's 128 output columns are exactly one scale block of the next GEMM's activation operand
+                            // and this lane holds its whole row: quantise here (same arithmetic as the standalone cast applied to
+                            // the BF16 values: power-of-two scale from the row's amax) and write e4m3 + the UE8M0 atom word.
+                            float amax = 0.f;
+#pragma unroll
+                            for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const int4 v4 = keep[ci][j];
+                                    const uint32_t w4[4] = {(uint32_t)v4.x, (uint32_t)v4.y, (uint32_t)v4.z, (uint32_t)v4.w};
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) {
+                                        const float2 f = bf16x2_to_f2(w4[t]);
+                                        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+                                    }
+                                }
+                            float scale, inv;
+                            fp8_scale_from_amax(amax, true, scale, inv);
+                            int4 q8[8];
+#pragma unroll
+                            for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+                                for (int jj = 0; jj < 2; ++jj) {
+                                    uint32_t outw[4];
+#pragma unroll
+                                    for (int h2 = 0; h2 < 2; ++h2) {
+                                        const int4 v4 = keep[ci][jj * 2 + h2];
+                                        const float2 f0 = bf16x2_to_f2((uint32_t)v4.x), f1 = bf16x2_to_f2((uint32_t)v4.y);
+                                        const float2 f2 = bf16x2_to_f2((uint32_t)v4.z), f3 = bf16x2_to_f2((uint32_t)v4.w);
+                                        outw[h2 * 2] = pack_e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+                                        outw[h2 * 2 + 1] = pack_e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
+                                    }
+                                    q8[ci * 2 + jj] = make_int4((int)outw[0], (int)outw[1], (int)outw[2], (int)outw[3]);
+                                }
+                            // 128 bytes per row go out like 64 BF16 columns: whole rows per store instruction
+                            uint8_t* obase = p.c_fp8 + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
+                            store_block_coalesced<64>(out_stage, q8, reinterpret_cast<__nv_bfloat16*>(obase), ldc / 2, rows_valid, lane);
+                            if (row < ti.c_row_end) {
+                                const uint32_t ex = (__float_as_uint(scale) >> 23) & 0xffu;
+                                *reinterpret_cast<uint32_t*>(p.c_atoms + ((size_t)(row >> 7) * (ldc / 128) + (ti.c_col >> 7)) * 512 + (row & 31) * 16 +
+                                                             ((row >> 5) & 3) * 4) = ex * 0x01010101u;
+                            }
+                            win_phase ^= 1;
+                            continue;
+                        }
+                    }
 #pragma unroll
                     for (int ci = 0; ci < C::kOutCols / 32; ++ci) store_block_coalesced<32>(out_stage, keep[ci], wbase + ci * 32, ldc, rows_valid, lane);
                     win_phase ^= 1;  // kWindows == 1: the same window, next phase

@@ -265,44 +265,65 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const __g
             // A lane owns 16 consecutive channels, 8 lanes own one scale group, a warp covers 512
             // channels per step.
             const char* src = reinterpret_cast<const char*>(a.x) + (size_t)t * H * 2;
-            for (int c0 = 0; c0 < H; c0 += 512) {
-                const int ch = c0 + lane * 16;
-                const bool act = ch < H;
-                int4 r0 = make_int4(0, 0, 0, 0), r1 = r0;
-                if (act) {
-                    r0 = ld_cached(reinterpret_cast<const int4*>(src + (size_t)ch * 2));
-                    r1 = ld_cached(reinterpret_cast<const int4*>(src + (size_t)ch * 2 + 16));
-                }
-                float f[16];
-                {
-                    const uint32_t w[8] = {(uint32_t)r0.x, (uint32_t)r0.y, (uint32_t)r0.z, (uint32_t)r0.w,
-                                           (uint32_t)r1.x, (uint32_t)r1.y, (uint32_t)r1.z, (uint32_t)r1.w};
+            // four 16-byte loads per lane in flight: the next 1024 channels are requested before the current ones are converted
+            int4 cur[4], nxt[4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float2 p = bf16x2_to_f2(w[j]);
-                        f[2 * j] = p.x;
-                        f[2 * j + 1] = p.y;
+            for (int h = 0; h < 2; ++h) {
+                const int ch = h * 512 + lane * 16;
+                cur[2 * h] = cur[2 * h + 1] = make_int4(0, 0, 0, 0);
+                if (ch < H) {
+                    cur[2 * h] = ld_cached(reinterpret_cast<const int4*>(src + (size_t)ch * 2));
+                    cur[2 * h + 1] = ld_cached(reinterpret_cast<const int4*>(src + (size_t)ch * 2 + 16));
+                }
+            }
+            for (int c0 = 0; c0 < H; c0 += 1024) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int chn = c0 + 1024 + h * 512 + lane * 16;
+                    nxt[2 * h] = nxt[2 * h + 1] = make_int4(0, 0, 0, 0);
+                    if (chn < H) {
+                        nxt[2 * h] = ld_cached(reinterpret_cast<const int4*>(src + (size_t)chn * 2));
+                        nxt[2 * h + 1] = ld_cached(reinterpret_cast<const int4*>(src + (size_t)chn * 2 + 16));
                     }
                 }
-                float amax = 0.f;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                float scale, inv;
-                fp8_scale_from_amax(amax, a.round_scale != 0, scale, inv);
-                int4 q;
-                q.x = (int)pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-                q.y = (int)pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-                q.z = (int)pack_e4m3x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
-                q.w = (int)pack_e4m3x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
-                if (act && (lane & 7) == 0) s_scales[warp][ch >> 7] = scale;
-                if (act) {
+                for (int h = 0; h < 2; ++h) {
+                    const int ch = c0 + h * 512 + lane * 16;
+                    const bool act = ch < H;
+                    const int4 r0 = cur[2 * h], r1 = cur[2 * h + 1];
+                    float f[16];
+                    {
+                        const uint32_t w[8] = {(uint32_t)r0.x, (uint32_t)r0.y, (uint32_t)r0.z, (uint32_t)r0.w,
+                                               (uint32_t)r1.x, (uint32_t)r1.y, (uint32_t)r1.z, (uint32_t)r1.w};
 #pragma unroll
-                    for (int d = 0; d < kMaxRanks; ++d)
-                        if (rows[d] >= 0) st_stream(reinterpret_cast<int4*>(s_dst[d].x + (size_t)rows[d] * H + ch), q);
+                        for (int j = 0; j < 8; ++j) {
+                            const float2 p = bf16x2_to_f2(w[j]);
+                            f[2 * j] = p.x;
+                            f[2 * j + 1] = p.y;
+                        }
+                    }
+                    float amax = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                    float scale, inv;
+                    fp8_scale_from_amax(amax, a.round_scale != 0, scale, inv);
+                    int4 q;
+                    q.x = (int)pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+                    q.y = (int)pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+                    q.z = (int)pack_e4m3x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+                    q.w = (int)pack_e4m3x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+                    if (act && (lane & 7) == 0) s_scales[warp][ch >> 7] = scale;
+                    if (act) {
+#pragma unroll
+                        for (int d = 0; d < kMaxRanks; ++d)
+                            if (rows[d] >= 0) st_stream(reinterpret_cast<int4*>(s_dst[d].x + (size_t)rows[d] * H + ch), q);
+                    }
                 }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
             }
             __syncwarp();
             for (int i = lane; i < num_scales; i += 32) {

@@ -306,6 +306,7 @@ UNIT_ROWS = 8  # rows of one expert a dispatch warp sends between two arrival-co
 # SM with a GEMM CTA of the natively block-scaled kernel (6 warps), but not with one of the promotion kernel (10 warps of 160
 # registers: three such warps fill a scheduler partition's quarter of the register file). A GEMM that got all SMs before the
 # dispatch CTAs were placed would then wait for rows that nobody can send, so some SMs are never given to it.
+FUSE_CAST_INTO_GEMM1 = True  # wide natively block-scaled tiles: GEMM1's epilogue emits e4m3 + scale atoms itself
 RESERVED_SMS_NATIVE = 4
 RESERVED_SMS_PROMOTE = 12
 GEMM_TIMEOUT_MS = 2000.0  # bound of every wait inside the gated GEMMs (pipeline barriers and arrival counters)
@@ -405,8 +406,13 @@ def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_
         sms1 = (148 - (RESERVED_SMS_NATIVE if native else RESERVED_SMS_PROMOTE)) if comm is not cur else 0
         if native:
             wide = R_ * w.num_tokens * K >= 512 * E
-            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, w.h, sms1, GEMM_TIMEOUT_MS, w.m_ends, w.recv_scales, l._mx[0 if wide else 2], **gate)
-            C.per_token_cast_to_fp8(w.h, True, False, None, 1, w.hq, w.hs, w.m_offsets[L:], True)
+            if wide and FUSE_CAST_INTO_GEMM1:
+                # a wide tile holds one whole scale block of the intermediate per row: the epilogue writes e4m3 + scale atoms itself
+                C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, None, sms1, GEMM_TIMEOUT_MS, w.m_ends, w.recv_scales, l._mx[0],
+                               out_fp8=w.hq, out_atoms=w.hs, **gate)
+            else:
+                C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, w.h, sms1, GEMM_TIMEOUT_MS, w.m_ends, w.recv_scales, l._mx[0 if wide else 2], **gate)
+                C.per_token_cast_to_fp8(w.h, True, False, None, 1, w.hq, w.hs, w.m_offsets[L:], True)
             C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, GEMM_TIMEOUT_MS, w.m_ends, w.hs, l._mx[1],
                            row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
         else:

@@ -239,3 +239,45 @@ def test_bf16_wgrad_reads_gradient_and_activation_in_place(rows, n_out, k_out):
             assert dw[g].float().abs().max().item() == 0
         else:
             assert _rel_err(dw[g], ref) < 1e-2, (g, _rel_err(dw[g], ref))
+
+
+def test_fp8_native_wide_swiglu_writes_quantised_output():
+    """The wide natively block-scaled SwiGLU kernel can emit e4m3 rows plus UE8M0 scale atoms itself; both must equal what
+    the standalone cast makes of the kernel's BF16 output, bit for bit (valid rows only; masked groups stay untouched)."""
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import build_sf_atoms_a, build_sf_atoms_b
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(21)
+    rows, K, N = [128, 200, 0, 384], 512, 1024  # N/2 = 512 outputs = 4 scale blocks per row
+    G = len(rows)
+    starts = [0]
+    for r in rows:
+        starts.append(starts[-1] + (r + 127) // 128 * 128)
+    M = starts[-1]
+    offs = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    ends = torch.tensor([starts[g] + rows[g] for g in range(G)], dtype=torch.int32, device="cuda")
+    x = torch.randn(M, K, device="cuda") * torch.pow(2.0, (torch.arange(M, device="cuda") % 5).float()).unsqueeze(1)
+    a, a_s = C.per_token_cast_to_fp8(x.to(torch.bfloat16), True, False)
+    w = torch.randn(G, N, K, device="cuda") * 0.1
+    wb = w.view(G, N // 128, 128, K // 128, 128)
+    b_s = torch.exp2(torch.ceil(torch.log2(wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0))).contiguous()
+    b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous()
+    sfa, sfb = build_sf_atoms_a(a_s), build_sf_atoms_b(b_s, N, True, True)
+    h = torch.zeros(M, N // 2, dtype=torch.bfloat16, device="cuda")
+    C.grouped_gemm(a, b, offs, 0, True, None, None, h, 0, 2000.0, ends, sfa, sfb)
+    hq_ref, atoms_ref = C.per_token_cast_to_fp8(h, True, False, None, 1, None, None, None, True)
+    hq = torch.full((M, N // 2), 0x55, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    atoms = torch.full(((M + 127) // 128, N // 2 // 128, 512), 0x55, dtype=torch.uint8, device="cuda")
+    C.grouped_gemm(a, b, offs, 0, True, None, None, None, 0, 2000.0, ends, sfa, sfb, out_fp8=hq, out_atoms=atoms)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    rr = torch.arange(M, device="cuda")
+    for g in range(G):
+        lo, hi = starts[g], starts[g] + rows[g]
+        assert torch.equal(hq.view(torch.uint8)[lo:hi], hq_ref.view(torch.uint8)[lo:hi]), g
+        assert (hq.view(torch.uint8)[hi:starts[g + 1]] == 0x55).all()
+        r = rr[lo:hi]
+        for kb in range(N // 2 // 128):
+            idx = (r % 32) * 16 + ((r // 32) % 4) * 4
+            assert torch.equal(atoms[r // 128, kb, idx], atoms_ref[r // 128, kb, idx]), (g, kb)

@@ -71,7 +71,7 @@ def main():
     xf, idxf, wf = x[:Tf].contiguous(), topk[:Tf].contiguous(), w[:Tf].contiguous()
     notify_args = [(idxf, fw.recv_x, fw.recv_scales_raw, fw.recv_info, fw.stage, fw.my_counts, fw.sel_list, fw.send_base, fw.unit_start,
                     fw.m_offsets, fw.m_ends, fw.peer_bases)]
-    disp_args = [(xf, fw.my_counts, fw.sel_list, fw.send_base, fw.unit_start, fw.peer_bases, None, None)]
+    disp_args = [(xf, fw.my_counts, fw.sel_list, fw.send_base, fw.unit_start, fw.peer_bases, None, None, None)]
 
     def em_dispatch():
         C.em_notify(rts, notify_args, E, UNIT_ROWS)

@@ -107,7 +107,8 @@ void em_notify(std::vector<py::object> rts, std::vector<py::tuple> per_rank, int
     check(dx::launch_em_notify(args.data(), V, at::cuda::getCurrentCUDAStream(core0->device()).stream()), "em_notify");
 }
 
-// Per rank tuple: (x, my_counts, sel_list, send_base, unit_start, peer_bases, dst_row|None, trace|None)
+// Per rank tuple: (x, my_counts, sel_list, send_base, unit_start, peer_bases, dst_row|None, trace|None, x_scales|None)
+// x is bf16 (rows are quantised by the kernel) or, with x_scales, e4m3 rows quantised beforehand (copied as they are).
 void em_dispatch(std::vector<py::object> rts, std::vector<py::tuple> per_rank, int num_experts, int num_topk, int unit_rows,
                  bool round_scale, bool native_atoms, int num_sms) {
     const int V = (int)rts.size();
@@ -119,15 +120,17 @@ void em_dispatch(std::vector<py::object> rts, std::vector<py::tuple> per_rank, i
     for (int v = 0; v < V; ++v) {
         dxh::RuntimeCore* core = dx_core_of(rts[v]);
         const py::tuple& t = per_rank[v];
-        DXF_CHECK(t.size() == 8, "em_dispatch: per-rank tuple must have 8 entries");
+        DXF_CHECK(t.size() == 9, "em_dispatch: per-rank tuple must have 9 entries");
         auto x = t[0].cast<torch::Tensor>();
         auto my_counts = t[1].cast<torch::Tensor>();
         auto sel_list = t[2].cast<torch::Tensor>();
         auto send_base = t[3].cast<torch::Tensor>();
         auto unit_start = t[4].cast<torch::Tensor>();
         auto peer_bases = t[5].cast<torch::Tensor>();
-        DXF_CHECK(x.is_cuda() && x.device().index() == core->device() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16 &&
-                      x.size(1) % 128 == 0, "x must be contiguous bf16 [T, hidden] on this rank's GPU with hidden % 128 == 0");
+        const bool prequant = !t[8].is_none();
+        DXF_CHECK(x.is_cuda() && x.device().index() == core->device() && x.dim() == 2 && x.is_contiguous() && x.size(1) % 128 == 0 &&
+                      (prequant ? x.element_size() == 1 : x.scalar_type() == torch::kBFloat16),
+                  "x must be contiguous [T, hidden] on this rank's GPU, hidden % 128 == 0: bf16, or e4m3 together with x_scales");
         const int64_t T = x.size(0);
         const auto dev = x.device();
         DXF_CHECK(i32_on(my_counts, dev, num_experts) && i32_on(sel_list, dev, (int64_t)num_experts * T) && i32_on(send_base, dev, num_experts) &&
@@ -135,7 +138,14 @@ void em_dispatch(std::vector<py::object> rts, std::vector<py::tuple> per_rank, i
         DXF_CHECK(peer_bases.is_cuda() && peer_bases.device() == dev && peer_bases.element_size() == 8 && peer_bases.numel() >= 4 * core->num_ranks(), "peer_bases must be 64-bit [4, R]");
         dx::EmDispatchArgs& a = args[v];
         a.ctx = core->ctx();
-        a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+        a.x = x.data_ptr();
+        a.x_scales = nullptr;
+        if (prequant) {
+            auto xs = t[8].cast<torch::Tensor>();
+            DXF_CHECK(xs.is_cuda() && xs.device() == dev && xs.scalar_type() == torch::kFloat32 && xs.is_contiguous() && xs.numel() == T * (x.size(1) / 128),
+                      "x_scales must be f32 [T, hidden/128] on x's GPU");
+            a.x_scales = xs.data_ptr<float>();
+        }
         a.num_tokens = (int)T;
         a.hidden = (int)x.size(1);
         a.num_topk = num_topk;

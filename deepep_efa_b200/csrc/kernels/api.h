@@ -156,7 +156,8 @@ cudaError_t launch_em_notify(const EmNotifyArgs* a, int num_virtual, cudaStream_
 
 struct EmDispatchArgs {
     RankCtx ctx;
-    const __nv_bfloat16* x;       // [T, hidden]
+    const void* x;                // [T, hidden] bf16 (quantised here), or e4m3 when x_scales is set (copied)
+    const float* x_scales;        // [T, hidden/128] f32 scales of pre-quantised rows (powers of two when native_atoms), or nullptr
     int num_tokens, hidden, num_topk, num_experts;
     int unit_rows, round_scale;
     int native_atoms;             // 1: scales are written as the UE8M0 words of [row tile][K block][512] scale atoms

@@ -8,7 +8,8 @@
 //               each of its experts will receive (added to a monotonic expectation that the GEMM compares with the
 //               arrival counter).
 //   em_dispatch a warp takes a unit of up to 8 rows of one expert, quantises each BF16 row to e4m3 (one scale per 128
-//               channels, as fp32 or as the UE8M0 words of the tensor core's scale atoms), stores it at its final row
+//               channels, as fp32 or as the UE8M0 words of the tensor core's scale atoms; or copies rows that were quantised
+//               once per token beforehand, which is what the overlapped layer does), stores it at its final row
 //               of the expert's rank, and bumps that expert's arrival counter with one release reduction. Units are
 //               issued expert-major (local expert index first, then destination rank), so on every rank expert 0
 //               completes first and the GEMM's group order equals the arrival order.
@@ -232,8 +233,42 @@ __global__ void __launch_bounds__(kEmDispatchThreads, 6) em_dispatch_kernel(cons
             const int t = sel / K;
             const int row = base_row + s;
             if (c.debug_extent != 0 && !peer_range_ok(c, d, dst_rows + (size_t)row * H, (size_t)H, 6)) continue;
-            const char* src = reinterpret_cast<const char*>(a.x) + (size_t)t * H * 2;
             char* drow = dst_rows + (size_t)row * H;
+            if (a.x_scales != nullptr) {
+                // rows quantised beforehand (once per token instead of once per selection): a pure copy, 4 KiB per pass
+                const int n16 = H / 16;
+                const int4* src16 = reinterpret_cast<const int4*>(reinterpret_cast<const char*>(a.x) + (size_t)t * H);
+                for (int i0 = 0; i0 < n16; i0 += 256) {
+                    int4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int i = i0 + u * 32 + lane;
+                        if (i < n16) v[u] = ld_cached(src16 + i);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int i = i0 + u * 32 + lane;
+                        if (i < n16) st_stream(reinterpret_cast<int4*>(drow) + i, v[u]);
+                    }
+                }
+                for (int kb = lane; kb < num_kb; kb += 32) {
+                    const float scale = a.x_scales[(size_t)t * num_kb + kb];
+                    if (a.native_atoms) {
+                        const uint32_t ex = (__float_as_uint(scale) >> 23) & 0xffu;
+                        *reinterpret_cast<uint32_t*>(dst_scales + ((size_t)(row >> 7) * num_kb + kb) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4) =
+                            ex * 0x01010101u;
+                    } else {
+                        reinterpret_cast<float*>(dst_scales)[(size_t)row * num_kb + kb] = scale;
+                    }
+                }
+                if (lane == 0) {
+                    info_base[d][row] = (me << 24) | sel;
+                    if (a.dst_row != nullptr) a.dst_row[sel] = row;
+                }
+                ++sent;
+                continue;
+            }
+            const char* src = reinterpret_cast<const char*>(a.x) + (size_t)t * H * 2;
             // a lane owns 16 consecutive channels, 8 lanes share a scale, a warp covers 512 channels per half step; the loads
             // of the next 1024 channels are issued before the current ones are converted
             int4 cur[4], nxt[4];

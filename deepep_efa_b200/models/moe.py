@@ -302,13 +302,16 @@ class MoELayer(nn.Module):
 # fused forward: expert-major dispatch -> arrival-gated GEMM1 -> cast -> GEMM2 with scatter epilogue -> local reduce
 # ---------------------------------------------------------------------------------------------------------
 UNIT_ROWS = 8  # rows of one expert a dispatch warp sends between two arrival-counter updates
-# SMs the arrival-gated GEMM leaves to the dispatch kernel when the two overlap. The dispatch CTAs are small enough to share an
-# SM with a GEMM CTA of the natively block-scaled kernel (6 warps), but not with one of the promotion kernel (10 warps of 160
-# registers: three such warps fill a scheduler partition's quarter of the register file). A GEMM that got all SMs before the
-# dispatch CTAs were placed would then wait for rows that nobody can send, so some SMs are never given to it.
+# SMs the arrival-gated GEMM leaves to the dispatch kernel while the two overlap. Sharing SMs cannot be relied on: a CTA of
+# the promotion kernel (10 warps of 160 registers) leaves no room for a dispatch warp in a scheduler partition's quarter of
+# the register file, and next to the natively block-scaled kernel the dispatch was measured several times slower than on
+# SMs of its own. A GEMM that got every SM before the dispatch CTAs were placed would wait for rows that nobody can send.
 FUSE_CAST_INTO_GEMM1 = True  # wide natively block-scaled tiles: GEMM1's epilogue emits e4m3 + scale atoms itself
-RESERVED_SMS_NATIVE = 4
-RESERVED_SMS_PROMOTE = 12
+RESERVED_SMS = 16
+# The gated GEMM runs as two launches when it overlaps the dispatch: the first part of the experts (arrival order = expert
+# order) on the SMs the dispatch does not use, the rest on all SMs once the dispatch is about done.
+SPLIT_FRACTION = 0.35
+PREQUANTIZE = True  # cast every token to e4m3 once before the dispatch, which then only copies rows (8 selections share a cast)
 GEMM_TIMEOUT_MS = 2000.0  # bound of every wait inside the gated GEMMs (pipeline barriers and arrival counters)
 
 
@@ -345,6 +348,8 @@ class _FusedWorkspace:
         self.hq = torch.empty(rows, I, dtype=torch.float8_e4m3fn, device=dev)
         self.hs = (torch.empty(rows // 128, I // 128, 512, dtype=torch.uint8, device=dev) if native
                    else torch.empty(rows, I // 128, dtype=torch.float32, device=dev))
+        self.xq = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=dev)
+        self.xs = torch.empty(T, H // 128, dtype=torch.float32, device=dev)
         C = layer._C()
         arrived, expected = C.em_gate_words(buf.runtime)
         self.arrived, self.expected = arrived[:L], expected[:L]
@@ -386,6 +391,9 @@ def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_
     native = wss[0].native
     cur = torch.cuda.current_stream()
     comm = bufs[0].comm_stream if (V == 1 and overlap) else cur
+    if PREQUANTIZE:
+        for x, w in zip(xs, wss):
+            C.per_token_cast_to_fp8(x, native, False, None, 1, w.xq, w.xs)
     if comm is not cur:
         comm.wait_stream(cur)
     with torch.cuda.stream(comm):
@@ -394,29 +402,42 @@ def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_
         planned = torch.cuda.Event()
         planned.record(comm)
         sms = num_dispatch_sms or (148 if V == 1 else max(1, 148 // V - 1))
-        C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None,
-                             None if w.trace is None else w.trace[0:2]) for x, w in zip(xs, wss)], E, K, UNIT_ROWS, native, native, sms)
+        C.em_dispatch(rts, [(w.xq if PREQUANTIZE else x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None,
+                             None if w.trace is None else w.trace[0:2], w.xs if PREQUANTIZE else None) for x, w in zip(xs, wss)],
+                      E, K, UNIT_ROWS, native, native, sms)
     if comm is not cur:
         cur.wait_event(planned)
     outs = []
     for l, w in zip(layers, wss):
         (w13, s13), (w2, s2) = l._fp8
         R_, L = l.buffer.group_size, l.num_local_experts
-        gate = dict(ready=w.arrived, expected=w.expected, trace=None if w.trace is None else w.trace[2:6])
-        sms1 = (148 - (RESERVED_SMS_NATIVE if native else RESERVED_SMS_PROMOTE)) if comm is not cur else 0
+        overlapped = comm is not cur
+        ga = min(L, max(1, int(round(L * SPLIT_FRACTION)))) if overlapped else L
         if native:
             wide = R_ * w.num_tokens * K >= 512 * E
-            if wide and FUSE_CAST_INTO_GEMM1:
-                # a wide tile holds one whole scale block of the intermediate per row: the epilogue writes e4m3 + scale atoms itself
-                C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, None, sms1, GEMM_TIMEOUT_MS, w.m_ends, w.recv_scales, l._mx[0],
-                               out_fp8=w.hq, out_atoms=w.hs, **gate)
+            sfb = l._mx[0 if wide else 2]
+            fuse_cast = wide and FUSE_CAST_INTO_GEMM1
+        # (first group, number of groups, SMs): the early experts next to the dispatch, the rest on the whole GPU
+        parts = [(0, ga, 148 - RESERVED_SMS), (ga, L - ga, 0)] if (overlapped and ga < L) else [(0, L, (148 - RESERVED_SMS) if overlapped else 0)]
+        for pi, (g0, ng, sms1) in enumerate(parts):
+            tr = None if (w.trace is None or pi > 0) else w.trace[2:6]
+            gate = dict(ready=w.arrived[g0:g0 + ng], expected=w.expected[g0:g0 + ng], trace=tr)
+            mo, me_ = w.m_offsets[g0:g0 + ng + 1], w.m_ends[g0:g0 + ng]
+            if native:
+                if fuse_cast:
+                    # a wide tile holds one whole scale block of the intermediate per row: the epilogue writes e4m3 + scale atoms itself
+                    C.grouped_gemm(w.recv_x, w13[g0:g0 + ng], mo, 0, True, None, None, None, sms1, GEMM_TIMEOUT_MS, me_, w.recv_scales, sfb[g0:g0 + ng],
+                                   out_fp8=w.hq, out_atoms=w.hs, **gate)
+                else:
+                    C.grouped_gemm(w.recv_x, w13[g0:g0 + ng], mo, 0, True, None, None, w.h, sms1, GEMM_TIMEOUT_MS, me_, w.recv_scales, sfb[g0:g0 + ng], **gate)
             else:
-                C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, None, None, w.h, sms1, GEMM_TIMEOUT_MS, w.m_ends, w.recv_scales, l._mx[0 if wide else 2], **gate)
+                C.grouped_gemm(w.recv_x, w13[g0:g0 + ng], mo, 0, True, w.recv_scales, s13[g0:g0 + ng], w.h, sms1, GEMM_TIMEOUT_MS, me_, None, None, **gate)
+        if native:
+            if not fuse_cast:
                 C.per_token_cast_to_fp8(w.h, True, False, None, 1, w.hq, w.hs, w.m_offsets[L:], True)
             C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, GEMM_TIMEOUT_MS, w.m_ends, w.hs, l._mx[1],
                            row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
         else:
-            C.grouped_gemm(w.recv_x, w13, w.m_offsets, 0, True, w.recv_scales, s13, w.h, sms1, GEMM_TIMEOUT_MS, w.m_ends, None, None, **gate)
             C.per_token_cast_to_fp8(w.h, False, False, None, 1, w.hq, w.hs, w.m_offsets[L:], False)
             C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, w.hs, s2, None, 0, GEMM_TIMEOUT_MS, w.m_ends, None, None,
                            row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])

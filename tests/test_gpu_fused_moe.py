@@ -50,8 +50,13 @@ def test_expert_major_dispatch_places_rows(R, T, H, E, K, native):
             C.em_notify(rts, [(i, w.recv_x, w.recv_scales_raw, w.recv_info, w.stage, w.my_counts, w.sel_list, w.send_base, w.unit_start,
                                w.m_offsets, w.m_ends, w.peer_bases) for i, w in zip(idxs, wss)], E, UNIT_ROWS)
             dst_rows = [torch.full((T * K,), -1, dtype=torch.int32, device="cuda") for _ in range(R)]
-            C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, dr, None)
-                                for x, w, dr in zip(xs, wss, dst_rows)], E, K, UNIT_ROWS, native, native, 8)
+            if rep == 0:   # rows quantised by the dispatch kernel itself
+                C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, dr, None, None)
+                                    for x, w, dr in zip(xs, wss, dst_rows)], E, K, UNIT_ROWS, native, native, 8)
+            else:          # rows quantised once per token beforehand, the dispatch only copies
+                pre = [C.per_token_cast_to_fp8(x, native, False) for x in xs]
+                C.em_dispatch(rts, [(q, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, dr, None, sc)
+                                    for (q, sc), w, dr in zip(pre, wss, dst_rows)], E, K, UNIT_ROWS, native, native, 8)
             torch.cuda.synchronize()
             for b in vc.buffers:
                 b.check_status()
@@ -144,7 +149,7 @@ def test_fused_dispatch_overflow_is_reported_not_written():
             w.recv_x.view(torch.uint8).fill_(7)
         C.em_notify(rts, [(i, w.recv_x, w.recv_scales_raw, w.recv_info, w.stage, w.my_counts, w.sel_list, w.send_base, w.unit_start,
                            w.m_offsets, w.m_ends, w.peer_bases) for i, w in zip(idxs, wss)], E, UNIT_ROWS)
-        C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None, None) for x, w in zip(xs, wss)],
+        C.em_dispatch(rts, [(x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None, None, None) for x, w in zip(xs, wss)],
                       E, K, UNIT_ROWS, False, False, 4)
         torch.cuda.synchronize()
         with pytest.raises(EPTimeoutError):

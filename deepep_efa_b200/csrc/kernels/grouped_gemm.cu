@@ -334,7 +334,9 @@ struct TileInfo {
     int a_mn0, a_kbase, b_mn0, b_kbase;
 };
 
-template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
+// kRowScatter: the scatter epilogue writes every output row of a 128-column tile as ONE 256-byte piece (the largest NVLink
+// packet) instead of two 128-byte pieces; it needs an 8 KiB staging buffer per epilogue warp and gives up one pipeline stage.
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false, bool kRowScatter = false>
 struct Cfg {
     static constexpr bool kPromote = kFp8 && !kMx;  // FP8 with fp32 scales: every K block is promoted on the CUDA cores
     static constexpr int kSfBAtoms = kBlockN / 128;                  // 512-byte scale atoms of the B tile
@@ -345,7 +347,7 @@ struct Cfg {
     static constexpr int kBTileBytes = kBRows * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes + kSfBytes;
     static constexpr int kStageTxBytes = kATileBytes + kBTileBytes + kSfTxBytes;  // bytes the copies of one stage deliver
-    static constexpr int kStages = kMx ? (kBlockN == 256 ? 4 : 6) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
+    static constexpr int kStages = kMx ? (kBlockN == 256 ? 4 : (kRowScatter ? 5 : 6)) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
     static constexpr int kTileRows = kPair ? 2 * kBlockM : kBlockM;  // rows of one scheduled tile (both CTAs of a pair)
     // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
     // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
@@ -360,15 +362,16 @@ struct Cfg {
     // of the columns); BF16 reads the accumulator once per tile and one warp per quarter is plenty.
     static constexpr int kEpiWarps = kPromote ? 8 : 4;
     static constexpr int kThreads = 64 + 32 * kEpiWarps;
-    static constexpr int kOutStageBytes = 4096;    // per epilogue warp: 32 rows x 64 BF16
+    static constexpr int kOutStageBytes = kRowScatter ? 8192 : 4096;    // per epilogue warp: 32 rows x 64 (128) BF16
     static constexpr size_t kSmemBytes =
         (size_t)kStages * kStageBytes + (size_t)kEpiWarps * kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
 };
 
-template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
-__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>::kThreads), 1)
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false, bool kRowScatter = false>
+__global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
-    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
+    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>;
+    static_assert(!kRowScatter || (kMx && !kSwiGLU && !kPair && kBlockN == 128), "whole-row scatter: natively block-scaled 128-column tiles");
     static_assert(!kMx || (kFp8 && !kPair && (kBlockN == 128 || (kBlockN == 256 && kSwiGLU))),
                   "native block scaling: e4m3 operands, single CTA, 128-column tiles (256 with SwiGLU)");
     const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader (issues the MMAs of the pair)
@@ -925,6 +928,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         store_block_coalesced<32>(out_stage, regs, wbase + c, ldc, rows_valid, lane);
                     }
+                } else if constexpr (kRowScatter) {
+                    // the tile's 128 columns of every row leave as one 256-byte piece: both halves go through the staging buffer
+                    // (32 rows x 16 pieces of 16 bytes, XOR-swizzled), then each store instruction covers two whole rows
+                    __syncwarp();
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 64) {
+                        uint32_t v[32], u[32];
+                        tmem_ld32(taddr + c, v);
+                        tmem_ld32(taddr + c + 32, u);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float o[8], o2[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                o[j] = __uint_as_float(v[i + j]);
+                                o2[j] = __uint_as_float(u[i + j]);
+                            }
+                            out_stage[lane * 16 + ((c / 8 + i / 8) ^ (lane & 15))] = pack8_bf16(o);
+                            out_stage[lane * 16 + ((c / 8 + 4 + i / 8) ^ (lane & 15))] = pack8_bf16(o2);
+                        }
+                    }
+                    __syncwarp();
+                    const unsigned long long mine = reinterpret_cast<unsigned long long>(scat_ptr);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int r2 = i * 2 + (lane >> 4), piece = lane & 15;
+                        const int4 val = out_stage[r2 * 16 + (piece ^ (r2 & 15))];
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, mine, r2));
+                        if (dst != nullptr) *reinterpret_cast<int4*>(dst + piece * 8) = val;
+                    }
                 } else {
 #pragma unroll 1
                     for (int c = 0; c < C::kOutCols; c += 64) {
@@ -1021,9 +1055,9 @@ bool make_map_mn(CUtensorMap* map, const void* ptr, uint64_t k_rows, uint64_t mn
     return r == CUDA_SUCCESS;
 }
 
-template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false>
+template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false, bool kRowScatter = false>
 cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
-    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
+    using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>;
     CUtensorMap map_a, map_b;
     const uint32_t b_box_rows = (kSwiGLU || kPair) ? kBlockN / 2 : kBlockN;
     bool ok;
@@ -1038,7 +1072,7 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
                      : make_map(&map_b, a.b, kFp8, (uint64_t)a.k, (uint64_t)a.m_total, b_box_rows));
     }
     if (!ok) return cudaErrorInvalidValue;
-    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU, kPair, kMx>;
+    auto kernel = grouped_gemm_kernel<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>;
     static bool smem_opted_in[64] = {};  // per device, once: the attribute is sticky
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1095,6 +1129,7 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
                 if (a.mx_wide) return launch_impl<256, true, true, false, true>(a, stream);
                 return launch_impl<128, true, true, false, true>(a, stream);
             }
+            if (a.row_info != nullptr) return launch_impl<128, true, false, false, true, true>(a, stream);
             return launch_impl<128, true, false, false, true>(a, stream);
         }
         if (a.fp8) {

@@ -158,6 +158,8 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
         if (pr != nullptr && (pr[0] == '0' || pr[0] == '1')) p.cta_pairs = pr[0] == '1';
         else p.cta_pairs = (!fp8 && p.m_ends == nullptr && (mode == 1 || (int64_t)p.m_total >= 1024 * (int64_t)G)) ? 1 : 0;
         if (p.num_sms < 2 || mn_major) p.cta_pairs = 0;
+        // natively block-scaled e4m3: a pair instantiation exists for the wide SwiGLU tile only
+        if (fp8 && !(p.sfa_atoms != nullptr && p.mx_wide == 1)) p.cta_pairs = (pr != nullptr && pr[0] == '1' && p.sfa_atoms == nullptr) ? 1 : 0;
     }
     if (ready.has_value() || expected.has_value()) {
         DXG_CHECK(mode == 0 && ready.has_value() && expected.has_value(), "ready and expected go together (M-grouped mode)");

@@ -22,6 +22,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstring>
+
 #include "gemm_api.h"
 #include "prims.cuh"
 
@@ -252,12 +254,25 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_
         : "memory");
 }
 // Instruction descriptor of the block-scaled kind: E4M3 operands (format 0), K-major, UE8M0 scales, scale-factor ids 0.
-__device__ __forceinline__ uint32_t make_idesc_mx(int n) {
+__device__ __forceinline__ uint32_t make_idesc_mx(int n, int m = kBlockM) {
     uint32_t d = 0;
     d |= (uint32_t)(n >> 3) << 17;         // N / 8
     d |= 1u << 23;                         // scale format: E8M0
-    d |= (uint32_t)(kBlockM >> 4) << 24;   // M / 16
+    d |= (uint32_t)(m >> 4) << 24;         // M / 16 (256 for a CTA pair)
     return d;
+}
+// CTA-pair forms: one instruction makes BOTH CTAs copy their own scale atoms (same shared-memory offset) into their own TMEM,
+// and one MMA covers the 256 rows of the pair; every CTA holds the scale factors of its own 128 rows of A and of ALL columns.
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mx_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
 }
 
 __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
@@ -347,7 +362,7 @@ struct Cfg {
     static constexpr int kBTileBytes = kBRows * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes + kSfBytes;
     static constexpr int kStageTxBytes = kATileBytes + kBTileBytes + kSfTxBytes;  // bytes the copies of one stage deliver
-    static constexpr int kStages = kMx ? (kBlockN == 256 ? 4 : (kRowScatter ? 5 : 6)) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
+    static constexpr int kStages = kMx ? ((kBlockN == 256 && !kPair) ? 4 : (kRowScatter ? 5 : 6)) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
     static constexpr int kTileRows = kPair ? 2 * kBlockM : kBlockM;  // rows of one scheduled tile (both CTAs of a pair)
     // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
     // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
@@ -369,11 +384,12 @@ struct Cfg {
 
 template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false, bool kRowScatter = false>
 __global__ void __launch_bounds__((Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>::kThreads), 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GroupedGemmArgs p) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, const GroupedGemmArgs p) {
     using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>;
     static_assert(!kRowScatter || (kMx && !kSwiGLU && !kPair && kBlockN == 128), "whole-row scatter: natively block-scaled 128-column tiles");
-    static_assert(!kMx || (kFp8 && !kPair && (kBlockN == 128 || (kBlockN == 256 && kSwiGLU))),
-                  "native block scaling: e4m3 operands, single CTA, 128-column tiles (256 with SwiGLU)");
+    static_assert(!kMx || (kFp8 && ((!kPair && kBlockN == 128) || (kBlockN == 256 && kSwiGLU))),
+                  "native block scaling: e4m3 operands, 128-column tiles, or 256-column SwiGLU tiles (single CTA or CTA pair)");
     const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader (issues the MMAs of the pair)
     const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -551,10 +567,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if constexpr (kPair) {
                         // both CTAs fill their own stage and signal the LEADER's barrier, which expects the bytes of both
                         const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0);
-                        if (cta_rank == 0) mbar_expect_tx(&full[stage], 2 * C::kStageBytes);
+                        if (cta_rank == 0) mbar_expect_tx(&full[stage], 2 * C::kStageTxBytes);
                         tma_load_2d_pair(&map_a, leader_full, sa, ti.a_k0 + kb * elem_per_kb, ti.a_row);
                         tma_load_2d_pair(&map_b, leader_full, sb, ti.b_k0 + kb * elem_per_kb,
                                          (kSwiGLU && cta_rank == 1) ? ti.b_row2 : ti.b_row);  // SwiGLU: gate half / up half
+                        if constexpr (kMx) {
+                            // scale atoms as rows of 32-bit words: this CTA's own 128 rows of A, and the whole tile's B columns
+                            uint8_t* ssf = sb + C::kBTileBytes;
+                            const int nkb = p.k / 128;
+                            tma_load_2d_pair(&map_sfa, leader_full, ssf, 0, (ti.a_row >> 7) * nkb + kb);
+                            tma_load_2d_pair(&map_sfb, leader_full, ssf + 512, 0, (ti.group * (p.n / kBlockN) + ti.nt) * nkb + kb);
+                        }
                         if (issued < C::kStages) ++issued;
                         if (++stage == C::kStages) {
                             stage = 0;
@@ -637,7 +660,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0 && cta_rank == 0) {
-            const uint32_t idesc = kMx ? make_idesc_mx(kBlockN) : make_idesc<kFp8>(kBlockN, C::kTileRows, p.a_mn, p.b_mn);
+            const uint32_t idesc = kMx ? make_idesc_mx(kBlockN, C::kTileRows) : make_idesc<kFp8>(kBlockN, C::kTileRows, p.a_mn, p.b_mn);
             // bytes (in 16-byte units) one K = 16 step moves the operand's start address: 32 B inside the swizzle atom when K
             // is contiguous, 16 K-steps of 128 B when the rows are
             const uint64_t a_kstep = p.a_mn ? 128 : 2, b_kstep = p.b_mn ? 128 : 2;
@@ -673,13 +696,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // scale atoms of this stage -> TMEM (alternating column sets), then four K=32 MMAs that read them
                         const uint32_t ssf = sb + C::kBTileBytes;
                         const uint32_t t_sfa = tmem_base + (uint32_t)(C::kSfCol0 + sf_buf * C::kSfColsPerBuf), t_sfb = t_sfa + 4;
-                        tmem_cp_sf(t_sfa, make_sf_desc(ssf));
+                        if constexpr (kPair) {
+                            tmem_cp_sf_pair(t_sfa, make_sf_desc(ssf));
 #pragma unroll
-                        for (int at = 0; at < C::kSfBAtoms; ++at) tmem_cp_sf(t_sfb + 4 * at, make_sf_desc(ssf + 512 + 512 * at));
+                            for (int at = 0; at < C::kSfBAtoms; ++at) tmem_cp_sf_pair(t_sfb + 4 * at, make_sf_desc(ssf + 512 + 512 * at));
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            umma_mx(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, t_sfa, t_sfb,
-                                    (new_window && j == 0) ? 0u : 1u);
+                            for (int j = 0; j < 4; ++j)
+                                umma_mx_pair(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, t_sfa, t_sfb,
+                                             (new_window && j == 0) ? 0u : 1u);
+                        } else {
+                            tmem_cp_sf(t_sfa, make_sf_desc(ssf));
+#pragma unroll
+                            for (int at = 0; at < C::kSfBAtoms; ++at) tmem_cp_sf(t_sfb + 4 * at, make_sf_desc(ssf + 512 + 512 * at));
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                umma_mx(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, t_sfa, t_sfb,
+                                        (new_window && j == 0) ? 0u : 1u);
+                        }
                         sf_buf ^= 1;
                     } else {
 #pragma unroll
@@ -1055,10 +1088,31 @@ bool make_map_mn(CUtensorMap* map, const void* ptr, uint64_t k_rows, uint64_t mn
     return r == CUDA_SUCCESS;
 }
 
+// Scale atoms as a 2-D tensor of 32-bit words: one row per (tile, K block), `words` words per row (128 per 512-byte atom).
+bool make_map_sf(CUtensorMap* map, const void* ptr, uint64_t rows, uint32_t words) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {words, rows};
+    cuuint64_t strides[1] = {(cuuint64_t)words * 4};
+    cuuint32_t box[2] = {words, 1};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false, bool kRowScatter = false>
 cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
     using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>;
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_sfa, map_sfb;
+    std::memset(&map_sfa, 0, sizeof(map_sfa));
+    std::memset(&map_sfb, 0, sizeof(map_sfb));
+    if constexpr (kMx && kPair) {
+        const uint64_t nkb = (uint64_t)a.k / 128;
+        if (!make_map_sf(&map_sfa, a.sfa_atoms, (((uint64_t)a.m_total + 127) / 128) * nkb, 128) ||
+            !make_map_sf(&map_sfb, a.sfb_atoms, (uint64_t)a.num_groups * (a.n / kBlockN) * nkb, 128 * C::kSfBAtoms))
+            return cudaErrorInvalidValue;
+    }
     const uint32_t b_box_rows = (kSwiGLU || kPair) ? kBlockN / 2 : kBlockN;
     bool ok;
     if (a.mode == 0) {
@@ -1095,9 +1149,9 @@ cudaError_t launch_impl(const GroupedGemmArgs& a, cudaStream_t stream) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         if (cfg.gridDim.x < 2) return cudaErrorInvalidValue;
-        return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, a);
+        return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, a);
     } else {
-        kernel<<<a.num_sms, C::kThreads, C::kSmemBytes, stream>>>(map_a, map_b, a);
+        kernel<<<a.num_sms, C::kThreads, C::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, a);
         return cudaGetLastError();
     }
 }
@@ -1126,6 +1180,7 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
             if (a.sfb_atoms == nullptr || a.k % 128 != 0 || a.n % 128 != 0) return cudaErrorInvalidValue;
             if (a.swiglu) {
                 if ((a.n / 2) % 128 != 0) return cudaErrorInvalidValue;  // gate/up halves start on scale-block boundaries
+                if (a.mx_wide && a.cta_pairs) return launch_impl<256, true, true, true, true>(a, stream);
                 if (a.mx_wide) return launch_impl<256, true, true, false, true>(a, stream);
                 return launch_impl<128, true, true, false, true>(a, stream);
             }

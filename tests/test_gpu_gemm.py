@@ -281,3 +281,40 @@ def test_fp8_native_wide_swiglu_writes_quantised_output():
         for kb in range(N // 2 // 128):
             idx = (r % 32) * 16 + ((r // 32) % 4) * 4
             assert torch.equal(atoms[r // 128, kb, idx], atoms_ref[r // 128, kb, idx]), (g, kb)
+
+
+def test_fp8_native_wide_swiglu_cta_pairs(monkeypatch):
+    """The wide natively block-scaled SwiGLU tile on CTA pairs (one 256-row MMA per pair, each CTA staging its own rows of A,
+    half of the B tile and its own copy of the scale atoms) gives the same numbers as the single-CTA kernel; rows carry
+    different power-of-two scales, so scale atoms that reached the wrong CTA's TMEM cannot pass."""
+    from deepep_efa_b200 import _ext
+    from deepep_efa_b200.ops.grouped_gemm import build_sf_atoms_a, build_sf_atoms_b, grouped_gemm, reference_grouped_gemm
+    C = _ext.load()
+    C.gemm_clear_error(0)
+    torch.manual_seed(31)
+    rows, K, N = [256, 512, 0, 384, 128], 1024, 1024
+    G = len(rows)
+    starts = [0]
+    for r in rows:
+        starts.append(starts[-1] + (r + 127) // 128 * 128)
+    M = starts[-1]
+    offs = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    x = torch.randn(M, K, device="cuda") * torch.pow(2.0, (torch.arange(M, device="cuda") % 7).float()).unsqueeze(1)
+    x = x * torch.pow(2.0, (torch.arange(K, device="cuda") // 128 % 3).float()).unsqueeze(0)
+    a, a_s = C.per_token_cast_to_fp8(x.to(torch.bfloat16), True, False)
+    w = torch.randn(G, N, K, device="cuda") * 0.1 * torch.pow(2.0, (torch.arange(N, device="cuda") // 128 % 4).float()).view(1, N, 1)
+    wb = w.view(G, N // 128, 128, K // 128, 128)
+    b_s = torch.exp2(torch.ceil(torch.log2(wb.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0))).contiguous()
+    b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous()
+    sfa, sfb = build_sf_atoms_a(a_s), build_sf_atoms_b(b_s, N, True, True)
+    monkeypatch.setenv("DEEPEP_GEMM_PAIR", "0")
+    single = grouped_gemm(a, b, offs, swiglu=True, sfa_atoms=sfa, sfb_atoms=sfb)
+    monkeypatch.setenv("DEEPEP_GEMM_PAIR", "1")
+    paired = grouped_gemm(a, b, offs, swiglu=True, sfa_atoms=sfa, sfb_atoms=sfb)
+    paired_small_grid = grouped_gemm(a, b, offs, swiglu=True, sfa_atoms=sfa, sfb_atoms=sfb, num_sms=6)
+    torch.cuda.synchronize()
+    assert C.gemm_error(0) == 0
+    ref = reference_grouped_gemm(a, b, offs, swiglu=True, a_scales=a_s, b_scales=b_s)
+    assert _rel_err(single, ref) < 1.5e-2
+    assert _rel_err(paired, ref) < 1.5e-2, _rel_err(paired, ref)
+    assert torch.equal(paired, single) and torch.equal(paired_small_grid, single)

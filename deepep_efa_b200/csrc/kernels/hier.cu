@@ -136,24 +136,43 @@ cudaError_t launch_recv_src_meta(const RecvSrcMetaArgs& a, cudaStream_t stream) 
     return cudaGetLastError();
 }
 
-__global__ void segmented_copy_kernel(const SegmentedCopyArgs a) {
-    for (int s = blockIdx.x; s < a.num_segments; s += gridDim.x) {
+// Segments are cut into 32 KiB chunks and the chunks of all segments are dealt round-robin to the CTAs, so that a few
+// large segments (one per node in the two-level path) use the whole grid as well as many small ones do.
+constexpr int64_t kSegChunk = 32 << 10;
+
+__global__ void __launch_bounds__(256) segmented_copy_kernel(const SegmentedCopyArgs a) {
+    const int64_t G = gridDim.x;
+    int64_t base = 0;  // chunks of the segments before s
+    for (int s = 0; s < a.num_segments; ++s) {
         const int64_t so = a.segments[3 * (size_t)s], d_o = a.segments[3 * (size_t)s + 1], n = a.segments[3 * (size_t)s + 2];
+        const int64_t chunks = (n + kSegChunk - 1) / kSegChunk;
         const uint8_t* src = a.src + so;
         uint8_t* dst = a.dst + d_o;
-        if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
-            const int64_t n16 = n / 16;
-            for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<int4*>(dst)[i] = ld_stream(reinterpret_cast<const int4*>(src) + i);
-            for (int64_t i = n16 * 16 + threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
-        } else {
-            for (int64_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+        const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+        for (int64_t c = ((int64_t)blockIdx.x - base % G + G) % G; c < chunks; c += G) {
+            const int64_t lo = c * kSegChunk, len = n - lo < kSegChunk ? n - lo : kSegChunk;
+            if (vec) {
+                const int4* s4 = reinterpret_cast<const int4*>(src + lo);
+                int4* d4 = reinterpret_cast<int4*>(dst + lo);
+                const int64_t n16 = len / 16;
+                int64_t i = threadIdx.x;
+                for (; i + 3 * 256 < n16; i += 4 * 256) {
+                    const int4 v0 = ld_stream(s4 + i), v1 = ld_stream(s4 + i + 256), v2 = ld_stream(s4 + i + 512), v3 = ld_stream(s4 + i + 768);
+                    d4[i] = v0, d4[i + 256] = v1, d4[i + 512] = v2, d4[i + 768] = v3;
+                }
+                for (; i < n16; i += 256) d4[i] = ld_stream(s4 + i);
+                for (int64_t j = n16 * 16 + threadIdx.x; j < len; j += 256) dst[lo + j] = src[lo + j];
+            } else {
+                for (int64_t j = threadIdx.x; j < len; j += 256) dst[lo + j] = src[lo + j];
+            }
         }
+        base += chunks;
     }
 }
 
 cudaError_t launch_segmented_copy(const SegmentedCopyArgs& a, cudaStream_t stream) {
     if (a.num_segments == 0) return cudaSuccess;
-    segmented_copy_kernel<<<a.num_segments < 1184 ? a.num_segments : 1184, 256, 0, stream>>>(a);
+    segmented_copy_kernel<<<1184, 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

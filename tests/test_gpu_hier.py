@@ -43,10 +43,12 @@ def test_layout_with_domains(T, E, R, P):
 def test_segmented_copy():
     from deepep_efa_b200.ops import hier as H
     torch.manual_seed(3)
-    src = torch.randint(0, 255, (1 << 16,), dtype=torch.uint8)
-    segs = torch.tensor([[0, 16, 4096], [5000, 9001, 333], [8192, 32768, 16384], [7, 60000, 1], [100, 61000, 0]])
-    want = torch.zeros(1 << 16, dtype=torch.uint8)
+    src = torch.randint(0, 255, (1 << 20,), dtype=torch.uint8)
+    # short and empty segments, an unaligned one, and two that span several 32 KiB chunks (one aligned, one not, ragged tails)
+    segs = torch.tensor([[0, 16, 4096], [5000, 9001, 333], [8192, 32768, 16384], [7, 60000, 1], [100, 61000, 0],
+                         [65536, 131072, 200000 + 48], [300001, 400003, 100001]])
+    want = torch.zeros(1 << 20, dtype=torch.uint8)
     H.segmented_copy(src, want, segs)
-    got = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    got = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
     H.segmented_copy(src.cuda(), got, segs.cuda())
     assert torch.equal(got.cpu(), want)

@@ -195,8 +195,11 @@ def _bench_normal(deep_ep, buf, rank, world, flush, steps, warmup, B):
         deep_ep.Buffer.set_num_sms(32)
         cfg_d = deep_ep.Config(32, best["dispatch_fp8_cached"]["chunk"], 256)
         cfg_c = deep_ep.Config(32, best["combine_bf16"]["chunk"], 256)
-        for name, fn, nbytes in (("dispatch_fp8_cached_32sms", lambda: buf.dispatch(x_e4m3, handle=handle_ref, config=cfg_d), n_recv * H * 2 * (1 + 4 / 128) / 2),
-                                 ("combine_bf16_32sms", lambda: buf.combine(y, handle_ref, config=cfg_c), n_recv * H * 2)):
+        # a handle carries per-channel matrices, and the channel count follows the SM count: take a fresh one at 32 SMs
+        handle32 = buf.dispatch(x_e4m3, num_tokens_per_rank=per_rank, is_token_in_rank=in_rank, num_tokens_per_expert=per_expert,
+                                topk_idx=topk_idx, topk_weights=topk_w, config=cfg_d)[4]
+        for name, fn, nbytes in (("dispatch_fp8_cached_32sms", lambda: buf.dispatch(x_e4m3, handle=handle32, config=cfg_d), n_recv * H * 2 * (1 + 4 / 128) / 2),
+                                 ("combine_bf16_32sms", lambda: buf.combine(y, handle32, config=cfg_c), n_recv * H * 2)):
             for _ in range(warmup):
                 fn()
             ms = B.max_over_ranks(B.timed_loop(fn, steps, flush))

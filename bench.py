@@ -308,6 +308,7 @@ def run_ours(args):
     steps, warmup = args.steps, max(args.warmup, 3)
     ll_bytes = ep.Buffer.get_low_latency_rdma_size_hint(LL_TOKENS, HIDDEN, world, NUM_EXPERTS)
     nvl_bytes = ep.Config(32, 6, 256, 6, 128).get_nvl_buffer_size_hint(HIDDEN * 2, world, NORMAL_TOKENS) if not args.skip_normal else (2 << 20)
+    nvl_bytes += NUM_EXPERTS * LL_TOKENS * HIDDEN * 2 + (16 << 20)  # room for the stand-in expert output [L, world*T, hidden] in symmetric memory
     buf = ep.Buffer(group, num_nvl_bytes=nvl_bytes, num_rdma_bytes=ll_bytes, low_latency_mode=True, explicitly_destroy=True)
     flush = torch.empty(256 << 20, dtype=torch.int8, device="cuda")
 
@@ -315,7 +316,12 @@ def run_ours(args):
     x_h, idx_h, w_h = make_inputs(rank, LL_TOKENS)
     x, topk_idx, topk_w = x_h.cuda(), idx_h.cuda(), w_h.cuda()
     L = NUM_EXPERTS // world
-    sim_gemm_out = torch.randn(L, world * LL_TOKENS, HIDDEN, device="cuda").to(torch.bfloat16) * 0.1
+    # The stand-in for the expert GEMM's output. The headline step keeps it in symmetric memory (Buffer.empty_symmetric, where a
+    # user of this library lets the last expert GEMM write): the home ranks then pull the rows they need straight from it. The same
+    # values in an ordinary tensor (combine pushes them through a stage) are timed beside it as `ll_plain_tensor_us`.
+    sim_gemm_plain = torch.randn(L, world * LL_TOKENS, HIDDEN, device="cuda").to(torch.bfloat16) * 0.1
+    sim_gemm_out = buf.empty_symmetric([L, world * LL_TOKENS, HIDDEN], torch.bfloat16)
+    sim_gemm_out.copy_(sim_gemm_plain)
     out = torch.empty(LL_TOKENS, HIDDEN, dtype=torch.bfloat16, device="cuda")
 
     def ll_step():
@@ -344,8 +350,47 @@ def run_ours(args):
     ll_us = max_over_ranks(sum(ll_samples) / steps * 1e3)
     ll_spread = spread_us(ll_samples)
 
-    # the same pair with the expert outputs in the zero-copy combine buffer (where a fused expert GEMM writes them): the
-    # home ranks then pull the rows in place instead of receiving them through the stage
+    # the same pair with the expert outputs in an ordinary device tensor: must give the same bits
+    plain_us = None
+    if not args.skip_breakdown:
+        def ll_step_plain():
+            _, _, handle, _, _ = buf.low_latency_dispatch(x, topk_idx, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+            buf.low_latency_combine(sim_gemm_plain, topk_idx, topk_w, handle, out=out)
+
+        ll_step()
+        want = out.clone()
+        out.zero_()
+        ll_step_plain()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), "combine of an ordinary tensor differs from the combine of the symmetric one"
+        for _ in range(warmup):
+            ll_step_plain()
+        plain_us = round(max_over_ranks(timed_loop(ll_step_plain, max(10, min(steps, 200)), flush) * 1e3), 3)
+        buf.check_status(sync=True)
+
+    # phase stamps of one dispatch + combine pair (first and last CTA of each kernel, %globaltimer, µs from the start of dispatch)
+    stamps = None
+    if args.ll_stamps:
+        buf.runtime.enable_trace(True)
+        for _ in range(2):
+            dist.barrier()
+            torch.cuda.synchronize()
+            ll_step()
+            torch.cuda.synchronize()
+            tr = buf.runtime.read_trace()
+        base = tr[(4 * 2 + 0) * 16]
+        mine = {f"{name}_{'first' if slot == 0 else 'last'}_cta": [round((v - base) / 1e3, 2) if v else None for v in tr[(fam * 2 + slot) * 16:(fam * 2 + slot) * 16 + 7]]
+                for fam, name in ((4, "ll_dispatch"), (5, "ll_combine")) for slot in (0, 1)}
+        buf.runtime.enable_trace(False)
+        allst = [None] * world
+        dist.all_gather_object(allst, mine)
+        stamps = {"rank0": allst[0], f"rank{world - 1}": allst[-1],
+                  "legend": {"ll_dispatch_first_cta": "start, idx loaded, counts of lower ranks, rows known, rows stored, release done, exit",
+                             "ll_dispatch_last_cta": "start, -, counts sent, all counts, layout out, all rows in, exit",
+                             "ll_combine (pull)": "start, offset posted, -, -, peers' offsets known, rows reduced, exit"}}
+
+    # the same pair with the expert outputs in the zero-copy combine buffer (where the decode path's last GEMM writes them):
+    # pulled like the symmetric tensor, without the closing "readers done" round a caller-owned tensor needs
     zc_us = None
     if not args.skip_breakdown:
         for _ in range(2):  # both parities hold the stand-in GEMM output
@@ -362,7 +407,7 @@ def run_ours(args):
         out.zero_()
         ll_step_zero_copy()
         torch.cuda.synchronize()
-        assert torch.equal(out, want), "pull combine (zero-copy buffer) differs from the staged combine"
+        assert torch.equal(out, want), "combine from the zero-copy buffer differs from the combine of the caller's tensor"
         for _ in range(warmup):
             ll_step_zero_copy()
         zc_us = round(max_over_ranks(timed_loop(ll_step_zero_copy, max(10, min(steps, 200)), flush) * 1e3), 3)
@@ -466,7 +511,7 @@ def run_ours(args):
                 _, _, h, _, _ = buf.low_latency_dispatch(x, mi, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
                 buf.low_latency_combine(sim_gemm_out, mi, mw, h, out=out)
 
-            for _ in range(3):
+            for _ in range(max(warmup, 5)):
                 masked_step()
             masked[f"{int(frac * 100)}pct"] = round(max_over_ranks(timed_loop(masked_step, sub_steps, flush) * 1e3), 2)
 
@@ -507,7 +552,11 @@ def run_ours(args):
         "value_median": ll_spread["median"],
         "value_min": ll_spread["min"],
         "ll_zero_copy_us": zc_us,
-        "notes": "our arm passes out= (a preallocated result tensor); the reference's single-node path allocates its own",
+        "ll_plain_tensor_us": plain_us,
+        "ll_stamps_us": stamps,
+        "notes": "our arm passes out= (a preallocated result tensor) and keeps the stand-in expert output in symmetric memory "
+                 "(Buffer.empty_symmetric; home ranks pull from it; ll_plain_tensor_us is the same call on an ordinary tensor); "
+                 "the reference's single-node path allocates its own result and takes an ordinary tensor",
         "gpu_launches": 2 * steps,
         "ll_dispatch_us": None if disp_us is None else round(disp_us, 2),
         "ll_combine_us": None if comb_us is None else round(comb_us, 2),
@@ -628,6 +677,7 @@ def main():
     ap.add_argument("--skip-breakdown", action="store_true")
     ap.add_argument("--skip-moe", action="store_true", help="leave out the model-level extras (fused MoE forward, decode step, training step)")
     ap.add_argument("--moe-steps", type=int, default=5)
+    ap.add_argument("--ll-stamps", action="store_true", help="add the device-side phase stamps of one dispatch + combine pair")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

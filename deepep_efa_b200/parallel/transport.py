@@ -42,15 +42,45 @@ class Transport:
         raise NotImplementedError
 
 
+def group_moves_cuda_tensors(group: dist.ProcessGroup) -> bool:
+    """True when the group's backend list has an entry for CUDA tensors (``nccl`` or ``cpu:gloo,cuda:nccl``)."""
+    name = str(dist.get_backend(group)).lower()
+    try:
+        name += "," + str(dist.get_backend_config(group)).lower()
+    except Exception:  # older torch: the plain name is all there is
+        pass
+    return "nccl" in name
+
+
 class CollectiveTransport(Transport):
-    """``torch.distributed.all_to_all_single`` over a process group (NCCL or gloo)."""
+    """``torch.distributed.all_to_all_single`` over a process group (NCCL or gloo).
+
+    A caller may hand the library a gloo group (it is all the bootstrap needs: ``all_gather_object`` and barriers). CUDA
+    tensors cannot travel over it, so the first CUDA tensor makes every member create, once, an NCCL group over the same
+    global ranks and use that from then on; the caller's group keeps serving CPU tensors. Same behaviour as the reference's
+    ``Buffer._get_gpu_group`` (deep_ep/buffer.py:228-265).
+    """
 
     name = "torch.distributed"
 
     def __init__(self, group: Optional[dist.ProcessGroup]) -> None:
         self.group = group
+        self._gpu_group: Optional[dist.ProcessGroup] = None
         self._size = group.size() if group is not None else 1
         self._rank = group.rank() if group is not None else 0
+
+    def group_for(self, t: torch.Tensor) -> Optional[dist.ProcessGroup]:
+        """The group that can move ``t``: the caller's, or the lazily created NCCL twin for CUDA tensors on a gloo group.
+        Collective over the group the first time a CUDA tensor arrives (every member moves the same kind of tensor)."""
+        if self.group is None or not t.is_cuda:
+            return self.group
+        if self._gpu_group is None:
+            if group_moves_cuda_tensors(self.group):
+                self._gpu_group = self.group
+            else:
+                ranks = dist.get_process_group_ranks(self.group)
+                self._gpu_group = dist.new_group(ranks=ranks, backend="nccl", use_local_synchronization=True)
+        return self._gpu_group
 
     def size(self) -> int:
         return self._size
@@ -68,7 +98,7 @@ class CollectiveTransport(Transport):
         if self._size == 1:
             out.copy_(rows)
             return out
-        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_splits, input_split_sizes=send_splits, group=self.group)
+        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_splits, input_split_sizes=send_splits, group=self.group_for(rows))
         return out
 
     def all_to_all_equal(self, t):
@@ -76,7 +106,7 @@ class CollectiveTransport(Transport):
         if self._size == 1:
             out.copy_(t)
             return out
-        dist.all_to_all_single(out, t.contiguous(), group=self.group)
+        dist.all_to_all_single(out, t.contiguous(), group=self.group_for(t))
         return out
 
 

@@ -165,6 +165,19 @@ def _worker(rank, world, port, q):
                 torch.cuda.synchronize()
                 buf.check_status(sync=True)
                 assert rel(yf, ref.detach()) < 8e-2, (native, rep, rel(yf, ref.detach()))
+        # ---- a gloo group handed to the rail transport: CUDA tensors travel over a lazily created NCCL twin ----
+        from deepep_efa_b200.parallel.transport import CollectiveTransport, group_moves_cuda_tensors
+        gloo = dist.new_group(backend="gloo")
+        dev = torch.device("cuda", rank)
+        assert not group_moves_cuda_tensors(gloo) and group_moves_cuda_tensors(dist.group.WORLD)
+        tr = CollectiveTransport(gloo)
+        blk = torch.full((world * 3, 5), float(rank), device=dev)
+        got = tr.all_to_all_equal(blk)
+        assert torch.equal(got, torch.arange(world, device=dev, dtype=blk.dtype).repeat_interleave(3)[:, None].expand(-1, 5))
+        assert tr.group_for(blk) is not gloo and tr.group_for(blk.cpu()) is gloo
+        sp = [r + 1 for r in range(world)]
+        rows = tr.all_to_all_rows(torch.full((sum(sp), 2), float(rank), device=dev), sp, [rank + 1] * world)
+        assert rows.shape[0] == (rank + 1) * world and torch.equal(rows[:, 0], torch.arange(world, device=dev, dtype=rows.dtype).repeat_interleave(rank + 1))
         buf.destroy()
         dist.destroy_process_group()
         q.put((rank, "ok"))

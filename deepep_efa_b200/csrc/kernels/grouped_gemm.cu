@@ -362,7 +362,7 @@ struct Cfg {
     static constexpr int kBTileBytes = kBRows * kKBlockBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes + kSfBytes;
     static constexpr int kStageTxBytes = kATileBytes + kBTileBytes + kSfTxBytes;  // bytes the copies of one stage deliver
-    static constexpr int kStages = kMx ? ((kBlockN == 256 && !kPair) ? 4 : (kRowScatter ? 5 : 6)) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
+    static constexpr int kStages = kMx ? ((kBlockN == 256) ? (kPair ? 5 : 4) : (kRowScatter ? 5 : 6)) : kPair ? ((kBlockN == 256) ? (kFp8 ? 5 : 6) : (kFp8 ? 6 : 8)) : ((kBlockN == 256) ? 4 : (kFp8 ? 5 : 6));
     static constexpr int kTileRows = kPair ? 2 * kBlockM : kBlockM;  // rows of one scheduled tile (both CTAs of a pair)
     // Accumulator windows in TMEM. FP8 hands the epilogue one window per K block, so the MMA warp needs to run several
     // K blocks ahead of the promotion: four 128-column windows fill TMEM. BF16 hands over one window per tile: two.
@@ -375,11 +375,16 @@ struct Cfg {
     static constexpr int kOutCols = kSwiGLU ? kBlockN / 2 : kBlockN;
     // FP8 promotes every K block on the CUDA cores, so it gets two epilogue warps per TMEM lane quarter (each takes half
     // of the columns); BF16 reads the accumulator once per tile and one warp per quarter is plenty.
-    static constexpr int kEpiWarps = kPromote ? 8 : 4;
+    // The single-window wide tile also gets two warps per quarter: each drains half of the columns RAW (128 fp32 registers per
+    // thread) and hands the window back at once, so the MMA issuer idles for the TMEM reads only, not for the SwiGLU arithmetic.
+    static constexpr bool kSplitDrain = kMx && kBlockN == 256;
+    static constexpr int kEpiWarps = (kPromote || kSplitDrain) ? 8 : 4;
     static constexpr int kThreads = 64 + 32 * kEpiWarps;
-    static constexpr int kOutStageBytes = kRowScatter ? 8192 : 4096;    // per epilogue warp: 32 rows x 64 (128) BF16
+    static constexpr int kOutStageBytes = kRowScatter ? 8192 : (kSplitDrain ? 2048 : 4096);    // per epilogue warp: 32 rows x 32 / 64 (128) BF16
+    // kSplitDrain with quantised output: the two warps of a quarter exchange their half-row maxima here (two tile parities)
+    static constexpr int kXchBytes = kSplitDrain ? 2 * 2 * kBlockM * 8 : 0;
     static constexpr size_t kSmemBytes =
-        (size_t)kStages * kStageBytes + (size_t)kEpiWarps * kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4;
+        (size_t)kStages * kStageBytes + (size_t)kEpiWarps * kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/ + (kMaxGroups + 1) * 4 + kXchBytes;
 };
 
 template <int kBlockN, bool kFp8, bool kSwiGLU, bool kPair, bool kMx = false, bool kRowScatter = false>
@@ -403,6 +408,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* tmem_full = bars + 2 * C::kStages; // [kWindows]
     uint64_t* tmem_empty = tmem_full + C::kWindows;  // [kWindows]
     int* tile_start = reinterpret_cast<int*>(bars + 32);  // [G+1] first tile index of every group
+    volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(bars + 32 + (kMaxGroups + 2) / 2);  // [2][2][kBlockM] (tile tag << 32 | amax bits)
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ volatile int s_prod_state[2];  // what the loader is doing (1 = arrival gate, 2 = free stage, 3 = loads issued) and for which tile
@@ -441,6 +447,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
         tile_start[G] = run;
+    }
+    if constexpr (C::kSplitDrain) {
+        for (int i = threadIdx.x; i < C::kXchBytes / 8; i += C::kThreads) xch[i] = 0ull;
     }
     if (warp == 1) {
         if constexpr (kPair) tmem_alloc_pair(&s_tmem_base, C::kTmemCols);
@@ -760,6 +769,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int row_in_tile = q * 32 + lane;
         int4* out_stage = reinterpret_cast<int4*>(out_stage_base + (size_t)(warp - 2) * C::kOutStageBytes);
         int g = 0, win = 0, win_phase = 0;
+        int xch_iter = 0;  // split drain: tiles whose row maxima went through the exchange so far
+        (void)xch_iter;
         TileInfo ti;
         bool ok = true;
         __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.c);
@@ -872,34 +883,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 __nv_bfloat16* wbase = cbase + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
                 const int rows_valid = min(32, ti.c_row_end - (ti.c_row + q * 32));
                 if constexpr (kSwiGLU && C::kWindows == 1) {
-                    // single window: the accumulator goes to registers (as BF16 outputs) first, the window returns to the MMA
-                    // issuer, and only then the stores run
-                    int4 keep[C::kOutCols / 32][4];
+                    // Single window, two warps per lane quarter: this warp takes 64 of the tile's 128 output columns. Their gate
+                    // and up accumulators go to registers raw, the window returns to the MMA issuer right away, and the
+                    // arithmetic and the stores run while the next tile accumulates.
+                    uint32_t v[2][32], u[2][32];
+                    tmem_ld32(taddr + half * 64, v[0]);
+                    tmem_ld32(taddr + half * 64 + 32, v[1]);
+                    tmem_ld32(taddr + kBlockN / 2 + half * 64, u[0]);
+                    tmem_ld32(taddr + kBlockN / 2 + half * 64 + 32, u[1]);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) release_window(&tmem_empty[win]);
+                    int4 keep[2][4];
 #pragma unroll
-                    for (int ci = 0; ci < C::kOutCols / 32; ++ci) {
-                        uint32_t v[32], u[32];
-                        tmem_ld32(taddr + ci * 32, v);
-                        tmem_ld32(taddr + kBlockN / 2 + ci * 32, u);
-                        tmem_ld_wait();
+                    for (int ci = 0; ci < 2; ++ci)
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
                             float o[8];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) o[j] = silu(__uint_as_float(v[i + j])) * __uint_as_float(u[i + j]);
+                            for (int j = 0; j < 8; ++j) o[j] = silu(__uint_as_float(v[ci][i + j])) * __uint_as_float(u[ci][i + j]);
                             keep[ci][i / 8] = pack8_bf16(o);
                         }
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) release_window(&tmem_empty[win]);
-                    if constexpr (kMx && C::kOutCols == 128) {
+                    if constexpr (kMx) {
                         if (p.c_fp8 != nullptr) {
-                            // The tile's 128 output columns are exactly one scale block of the next GEMM's activation operand
-                            // and this lane holds its whole row: quantise here (same arithmetic as the standalone cast applied to
-                            // the BF16 values: power-of-two scale from the row's amax) and write e4m3 + the UE8M0 atom word.
+                            // The tile's 128 output columns are exactly one scale block of the next GEMM's activation operand: quantise
+                            // here (same arithmetic as the standalone cast applied to the BF16 values: power-of-two scale from the
+                            // row's amax) and write e4m3 + the UE8M0 atom word. The row's other 64 columns sit in the partner warp
+                            // of this quarter; the two exchange their maxima through shared memory, tagged with the tile number.
                             float amax = 0.f;
 #pragma unroll
-                            for (int ci = 0; ci < 4; ++ci)
+                            for (int ci = 0; ci < 2; ++ci)
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const int4 v4 = keep[ci][j];
@@ -910,11 +924,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                         amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
                                     }
                                 }
+                            const int par = xch_iter & 1;
+                            ++xch_iter;
+                            const unsigned tag = (unsigned)tile + 1u;
+                            xch[(par * 2 + half) * kBlockM + row_in_tile] = ((unsigned long long)tag << 32) | __float_as_uint(amax);
+                            volatile unsigned long long* other = xch + (par * 2 + (half ^ 1)) * kBlockM + row_in_tile;
+                            unsigned long long w = *other;
+                            if ((unsigned)(w >> 32) != tag) {
+                                const long long t0 = clock64();
+                                while ((unsigned)((w = *other) >> 32) != tag) {
+                                    if (*abort_flag || clock64() - t0 > limit) {
+                                        if (!*abort_flag && note != nullptr) atomicCAS(note, 0ull, wait_id(7, tile, 0, warp));
+                                        *abort_flag = 1;
+                                        ok = false;
+                                        break;
+                                    }
+                                }
+                            }
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (!ok) break;
+                            amax = fmaxf(amax, __uint_as_float((unsigned)w));
                             float scale, inv;
                             fp8_scale_from_amax(amax, true, scale, inv);
-                            int4 q8[8];
+                            int4 q8[4];
 #pragma unroll
-                            for (int ci = 0; ci < 4; ++ci)
+                            for (int ci = 0; ci < 2; ++ci)
 #pragma unroll
                                 for (int jj = 0; jj < 2; ++jj) {
                                     uint32_t outw[4];
@@ -928,10 +962,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     }
                                     q8[ci * 2 + jj] = make_int4((int)outw[0], (int)outw[1], (int)outw[2], (int)outw[3]);
                                 }
-                            // 128 bytes per row go out like 64 BF16 columns: whole rows per store instruction
-                            uint8_t* obase = p.c_fp8 + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col;
-                            store_block_coalesced<64>(out_stage, q8, reinterpret_cast<__nv_bfloat16*>(obase), ldc / 2, rows_valid, lane);
-                            if (row < ti.c_row_end) {
+                            // 64 bytes per row go out like 32 BF16 columns: whole row pieces per store instruction
+                            uint8_t* obase = p.c_fp8 + (size_t)(ti.c_row + q * 32) * ldc + ti.c_col + half * 64;
+                            store_block_coalesced<32>(out_stage, q8, reinterpret_cast<__nv_bfloat16*>(obase), ldc / 2, rows_valid, lane);
+                            if (half == 0 && row < ti.c_row_end) {
                                 const uint32_t ex = (__float_as_uint(scale) >> 23) & 0xffu;
                                 *reinterpret_cast<uint32_t*>(p.c_atoms + ((size_t)(row >> 7) * (ldc / 128) + (ti.c_col >> 7)) * 512 + (row & 31) * 16 +
                                                              ((row >> 5) & 3) * 4) = ex * 0x01010101u;
@@ -941,7 +975,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
 #pragma unroll
-                    for (int ci = 0; ci < C::kOutCols / 32; ++ci) store_block_coalesced<32>(out_stage, keep[ci], wbase + ci * 32, ldc, rows_valid, lane);
+                    for (int ci = 0; ci < 2; ++ci) store_block_coalesced<32>(out_stage, keep[ci], wbase + half * 64 + ci * 32, ldc, rows_valid, lane);
                     win_phase ^= 1;  // kWindows == 1: the same window, next phase
                     continue;
                 } else if constexpr (kSwiGLU) {

@@ -35,6 +35,8 @@ def main():
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--tile", default="auto", choices=["auto", "wide", "narrow"],
+                    help="natively block-scaled fp8 only: 256- or 128-column tiles (auto: wide with --swiglu, narrow without)")
     ap.add_argument("--op", default="fwd", choices=["fwd", "dgrad", "wgrad", "wgrad_t"])
     ap.add_argument("--native-scaling", action="store_true",
                     help="fp8 only: power-of-two scales applied by the tensor core (UE8M0 block scaling) instead of per-K-block promotion")
@@ -58,7 +60,7 @@ def main():
         b = (wb / b_s.view(G, N // 128, 1, K // 128, 1)).view(G, N, K).to(torch.float8_e4m3fn).contiguous()
         del wb
         if args.native_scaling:
-            atoms_b = build_sf_atoms_b(b_s, N, args.swiglu)  # once per weight
+            atoms_b = build_sf_atoms_b(b_s, N, args.swiglu, None if args.tile == "auto" else args.tile == "wide")  # once per weight
             # the activation atoms are rebuilt on every call, as a layer does
             fn = lambda: grouped_gemm(a, b, offs, swiglu=args.swiglu, sfa_atoms=build_sf_atoms_a(a_s), sfb_atoms=atoms_b)
         else:

@@ -116,7 +116,8 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const
                           sfa_atoms->numel() >= ((M + 127) / 128) * (K / 128) * 512, "sfa_atoms must be uint8 [ceil(M/128), K/128, 512]");
             DXG_CHECK(sfb_atoms->is_cuda() && sfb_atoms->scalar_type() == torch::kUInt8 && sfb_atoms->is_contiguous() &&
                           sfb_atoms->numel() == (int64_t)G * atoms_n * (K / 128) * 512, "sfb_atoms must be uint8 [G, N/128 atoms, K/128, 512]");
-            p.mx_wide = (swiglu && sfb_atoms->size(-1) == 1024) ? 1 : 0;  // the atom layout says which tile width it was built for
+            p.mx_wide = sfb_atoms->size(-1) == 1024 ? 1 : 0;  // the atom layout says which tile width it was built for
+            DXG_CHECK(!p.mx_wide || swiglu || N % 256 == 0, "scale atoms built for 256-column tiles need N % 256 == 0");
             p.sfa_atoms = sfa_atoms->data_ptr<uint8_t>();
             p.sfb_atoms = sfb_atoms->data_ptr<uint8_t>();
         } else if (fp8) {
@@ -327,8 +328,8 @@ torch::Tensor build_sf_atoms_b(const torch::Tensor& scales, int64_t n, bool swig
     c10::cuda::CUDAGuard guard(scales.device());
     const int64_t G = scales.size(0), nkb = scales.size(2);
     DXG_CHECK(!swiglu || (n / 2) % 128 == 0, "build_sf_atoms_b: swiglu needs N/2 % 128 == 0");
-    wide = wide && swiglu;
-    const int64_t tiles = swiglu ? (wide ? (n / 2) / 128 : (n / 2) / 64) : n / 128;
+    DXG_CHECK(swiglu || !wide || n % 256 == 0, "build_sf_atoms_b: 256-column tiles need N % 256 == 0");
+    const int64_t tiles = swiglu ? (wide ? (n / 2) / 128 : (n / 2) / 64) : (wide ? n / 256 : n / 128);
     auto atoms = torch::empty({G, tiles, nkb, wide ? 1024 : 512}, scales.options().dtype(torch::kUInt8));
     const cudaError_t e = dx::launch_build_sfb_atoms(scales.data_ptr<float>(), atoms.data_ptr<uint8_t>(), (int)G, (int)n, (int)nkb, swiglu ? 1 : 0, wide ? 1 : 0,
                                                      at::cuda::getCurrentCUDAStream(scales.get_device()).stream());
@@ -338,7 +339,7 @@ torch::Tensor build_sf_atoms_b(const torch::Tensor& scales, int64_t n, bool swig
 
 void bind_gemm(py::module_& m) {
     m.def("build_sf_atoms_a", &build_sf_atoms_a);
-    m.def("build_sf_atoms_b", &build_sf_atoms_b, py::arg("scales"), py::arg("n"), py::arg("swiglu") = false, py::arg("wide") = true);
+    m.def("build_sf_atoms_b", &build_sf_atoms_b, py::arg("scales"), py::arg("n"), py::arg("swiglu") = false, py::arg("wide") = false);
     m.def("transpose_bf16", &transpose_bf16);
     m.def("swiglu_fwd", &swiglu_fwd);
     m.def("swiglu_bwd", &swiglu_bwd);

@@ -341,6 +341,29 @@ __device__ __forceinline__ void store_block_scattered(int4* stage, const int4 (&
     }
 }
 
+// 32 rows x 256 bytes: lane l holds row l as 16 pieces of 16 bytes, and the row's destination (nullptr = drop the row). Eight rows at a
+// time pass through a 2 KiB staging buffer (XOR-swizzled pieces), so that every store instruction covers two whole 256-byte rows:
+// rows that leave for another GPU cross NVLink in 256-byte packets.
+__device__ __forceinline__ void store_rows_256(int4* stage, const int4 (&regs)[16], __nv_bfloat16* my_row_ptr, int lane) {
+    const unsigned long long mine = reinterpret_cast<unsigned long long>(my_row_ptr);
+#pragma unroll
+    for (int g8 = 0; g8 < 4; ++g8) {
+        __syncwarp();
+        if ((lane >> 3) == g8) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) stage[(lane & 7) * 16 + (j ^ (lane & 7))] = regs[j];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r8 = i * 2 + (lane >> 4), piece = lane & 15;
+            const int4 v = stage[r8 * 16 + (piece ^ r8)];
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, mine, g8 * 8 + r8));
+            if (dst != nullptr) *reinterpret_cast<int4*>(dst + piece * 8) = v;
+        }
+    }
+}
+
 struct TileInfo {
     int a_row, a_k0, b_row, b_row2, b_k0, num_kb, c_row, c_col, group, nblock, nblock2;
     int c_row_end;  // first output row this tile must not write (end of its group; groups need no 128-row alignment)
@@ -393,8 +416,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, const GroupedGemmArgs p) {
     using C = Cfg<kBlockN, kFp8, kSwiGLU, kPair, kMx, kRowScatter>;
     static_assert(!kRowScatter || (kMx && !kSwiGLU && !kPair && kBlockN == 128), "whole-row scatter: natively block-scaled 128-column tiles");
-    static_assert(!kMx || (kFp8 && ((!kPair && kBlockN == 128) || (kBlockN == 256 && kSwiGLU))),
-                  "native block scaling: e4m3 operands, 128-column tiles, or 256-column SwiGLU tiles (single CTA or CTA pair)");
+    static_assert(!kMx || (kFp8 && ((!kPair && kBlockN == 128) || (kBlockN == 256 && (kSwiGLU || !kPair)))),
+                  "native block scaling: e4m3 operands; 128-column tiles, 256-column tiles, or 256-column SwiGLU tiles on a CTA pair");
     const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader (issues the MMAs of the pair)
     const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -995,6 +1018,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         store_block_coalesced<32>(out_stage, regs, wbase + c, ldc, rows_valid, lane);
                     }
+                } else if constexpr (C::kSplitDrain) {
+                    // 256-column tile, single window, two warps per lane quarter: this warp takes 128 of the columns. They go to
+                    // registers raw, the window returns to the MMA issuer, then every row leaves as one 256-byte piece (to the
+                    // output matrix, or with the scatter epilogue to the row its info word names).
+                    uint32_t v[4][32];
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) tmem_ld32(taddr + half * 128 + c4 * 32, v[c4]);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) release_window(&tmem_empty[win]);
+                    int4 regs[16];
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float o[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(v[c4][i + j]);
+                            regs[c4 * 4 + i / 8] = pack8_bf16(o);
+                        }
+                    __nv_bfloat16* dst = scatter ? (scat_ptr != nullptr ? scat_ptr + half * 128 : nullptr) : (row < ti.c_row_end ? crow + half * 128 : nullptr);
+                    store_rows_256(out_stage, regs, dst, lane);
+                    win_phase ^= 1;  // kWindows == 1: the same window, next phase
+                    continue;
                 } else if constexpr (kRowScatter) {
                     // the tile's 128 columns of every row leave as one 256-byte piece: both halves go through the staging buffer
                     // (32 rows x 16 pieces of 16 bytes, XOR-swizzled), then each store instruction covers two whole rows
@@ -1218,6 +1266,7 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
                 if (a.mx_wide) return launch_impl<256, true, true, false, true>(a, stream);
                 return launch_impl<128, true, true, false, true>(a, stream);
             }
+            if (a.mx_wide) return (a.n % 256 == 0) ? launch_impl<256, true, false, false, true>(a, stream) : cudaErrorInvalidValue;
             if (a.row_info != nullptr) return launch_impl<128, true, false, false, true, true>(a, stream);
             return launch_impl<128, true, false, false, true>(a, stream);
         }

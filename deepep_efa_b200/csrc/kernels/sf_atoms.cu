@@ -60,6 +60,12 @@ __global__ void sfb_atoms_kernel(const float* __restrict__ scales, uint8_t* __re
             const uint32_t wu = ue8m0_word(scales[(g * nb + nb / 2 + t) * num_kb + kb]);
             *reinterpret_cast<uint4*>(atoms + tk * 1024 + m0 * 16) = make_uint4(wg, wg, wg, wg);
             *reinterpret_cast<uint4*>(atoms + tk * 1024 + 512 + m0 * 16) = make_uint4(wu, wu, wu, wu);
+        } else if (wide) {
+            // 256-column tiles without SwiGLU: the atoms of the two neighbouring 128-row blocks side by side
+            const uint32_t w0 = ue8m0_word(scales[(g * nb + 2 * t) * num_kb + kb]);
+            const uint32_t w1 = ue8m0_word(scales[(g * nb + 2 * t + 1) * num_kb + kb]);
+            *reinterpret_cast<uint4*>(atoms + tk * 1024 + m0 * 16) = make_uint4(w0, w0, w0, w0);
+            *reinterpret_cast<uint4*>(atoms + tk * 1024 + 512 + m0 * 16) = make_uint4(w1, w1, w1, w1);
         } else {
             const uint32_t wv = ue8m0_word(scales[(g * nb + t) * num_kb + kb]);
             *reinterpret_cast<uint4*>(atoms + tk * 512 + m0 * 16) = make_uint4(wv, wv, wv, wv);
@@ -80,8 +86,8 @@ cudaError_t launch_build_sfa_atoms(const float* scales, uint8_t* atoms, int rows
 
 cudaError_t launch_build_sfb_atoms(const float* scales, uint8_t* atoms, int groups, int n, int num_kb, int swiglu, int wide,
                                    cudaStream_t stream) {
-    if (n % 128 != 0 || (swiglu && (n / 2) % 128 != 0)) return cudaErrorInvalidValue;
-    const int tiles = swiglu ? (wide ? (n / 2) / 128 : (n / 2) / 64) : n / 128;
+    if (n % 128 != 0 || (swiglu && (n / 2) % 128 != 0) || (!swiglu && wide && n % 256 != 0)) return cudaErrorInvalidValue;
+    const int tiles = swiglu ? (wide ? (n / 2) / 128 : (n / 2) / 64) : (wide ? n / 256 : n / 128);
     const long long total = (long long)groups * tiles * num_kb * 32;
     if (total <= 0) return cudaSuccess;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);

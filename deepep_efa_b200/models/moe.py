@@ -190,9 +190,11 @@ class MoELayer(nn.Module):
         if native_block_scaling:
             (_, s13), (_, s2) = self._fp8
             n13 = self.w13.size(1)
-            # (wide tiles for large groups, narrow tiles for small groups / decode, second GEMM)
-            self._mx = (gg.build_sf_atoms_b(s13, n13, swiglu=True, wide=True), gg.build_sf_atoms_b(s2, self.w2.size(1)),
-                        gg.build_sf_atoms_b(s13, n13, swiglu=True, wide=False))
+            # (first GEMM wide tiles for large groups, second GEMM narrow, first GEMM narrow for small groups / decode, second GEMM wide)
+            n2 = self.w2.size(1)
+            self._mx = (gg.build_sf_atoms_b(s13, n13, swiglu=True, wide=True), gg.build_sf_atoms_b(s2, n2, wide=False),
+                        gg.build_sf_atoms_b(s13, n13, swiglu=True, wide=False),
+                        gg.build_sf_atoms_b(s2, n2, wide=True) if n2 % 256 == 0 else gg.build_sf_atoms_b(s2, n2, wide=False))
 
     @torch.no_grad()
     def forward_fp8(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -218,7 +220,7 @@ class MoELayer(nn.Module):
             wide = plan.num_rows >= 512 * self.num_local_experts
             h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, sfa_atoms=gg.build_sf_atoms_a(a_s), sfb_atoms=mx[0 if wide else 2])
             hq, hs = C.per_token_cast_to_fp8(h, True, False)
-            y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, sfa_atoms=gg.build_sf_atoms_a(hs), sfb_atoms=mx[1])
+            y_perm = gg.grouped_gemm(hq, w2, plan.m_offsets, sfa_atoms=gg.build_sf_atoms_a(hs), sfb_atoms=mx[3 if wide else 1])
         else:
             h = gg.grouped_gemm(a, w13, plan.m_offsets, swiglu=True, a_scales=a_s, b_scales=s13)
             hq, hs = C.per_token_cast_to_fp8(h, False, False)
@@ -435,7 +437,7 @@ def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_
         if native:
             if not fuse_cast:
                 C.per_token_cast_to_fp8(w.h, True, False, None, 1, w.hq, w.hs, w.m_offsets[L:], True)
-            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, GEMM_TIMEOUT_MS, w.m_ends, w.hs, l._mx[1],
+            C.grouped_gemm(w.hq, w2, w.m_offsets, 0, False, None, None, None, 0, GEMM_TIMEOUT_MS, w.m_ends, w.hs, l._mx[3 if wide else 1],
                            row_info=w.recv_info, scatter_bases=w.peer_bases[3 * R_:])
         else:
             C.per_token_cast_to_fp8(w.h, False, False, None, 1, w.hq, w.hs, w.m_offsets[L:], False)

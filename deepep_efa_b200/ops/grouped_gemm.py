@@ -42,13 +42,16 @@ def build_sf_atoms_a(a_scales: torch.Tensor) -> torch.Tensor:
     return _ext.load().build_sf_atoms_a(a_scales.contiguous())
 
 
-def build_sf_atoms_b(b_scales: torch.Tensor, n: int, swiglu: bool = False, wide: bool = True) -> torch.Tensor:
+def build_sf_atoms_b(b_scales: torch.Tensor, n: int, swiglu: bool = False, wide: Optional[bool] = None) -> torch.Tensor:
     """UE8M0 scale atoms of the weights (``b_scales`` f32 ``[G, N/128, K/128]``, powers of two); built once per weight.
 
-    With ``swiglu`` the atoms also fix the tile width of the GEMM that consumes them: ``wide=True`` is the 256-column tile
-    with one accumulator window (fastest for several hundred rows per expert and more), ``wide=False`` the 128-column tile
-    with two windows (better for small groups and for the masked low-latency layout)."""
-    return _ext.load().build_sf_atoms_b(b_scales.contiguous(), n, swiglu, wide)
+    The atoms also fix the tile width of the GEMM that consumes them: ``wide=True`` is the 256-column tile with one
+    accumulator window (fastest for several hundred rows per expert and more; without ``swiglu`` it needs ``N % 256 == 0``),
+    ``wide=False`` the 128-column tile with two windows (better for small groups and for the masked low-latency layout).
+    Default: wide with ``swiglu``, narrow without."""
+    if wide is None:
+        wide = swiglu
+    return _ext.load().build_sf_atoms_b(b_scales.contiguous(), n, swiglu, bool(wide))
 
 
 def grouped_gemm_wgrad(a_t: torch.Tensor, b_t: torch.Tensor, m_offsets: torch.Tensor, *, out: Optional[torch.Tensor] = None,

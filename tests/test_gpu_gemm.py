@@ -168,7 +168,7 @@ def test_rowdot_kernel():
     assert torch.allclose(got, want, rtol=1e-3, atol=1e-2)
 
 
-@pytest.mark.parametrize("swiglu,wide", [(False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("swiglu,wide", [(False, True), (False, False), (True, True), (True, False)])
 def test_fp8_native_block_scaling(swiglu, wide):
     """tcgen05 block-scaled MMA with UE8M0 scale atoms against the dequantised fp32 reference; the row scales differ by
     powers of two from row to row so that a wrong row-to-scale mapping cannot pass."""

@@ -848,12 +848,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         continue;
                     }
-                    const float sa = __ldcg(sa_row + kb);  // L2 only: with arrival gating these scales were written by other GPUs during this kernel
-                    const float s_lo = sa * __ldg(sb0 + kb), s_hi = kSwiGLU ? sa * __ldg(sb1 + kb) : s_lo;
+                    // Ungated: the activation scale is fetched ahead of the wait, to hide its latency. With arrival gating the
+                    // scales are written by other GPUs during this kernel, and only the accumulator hand-over orders this warp
+                    // after the loader's acquire of the group's arrival counter: the load has to come after the wait (L2 only).
+                    float sa = 0.f;
+                    if (p.ready == nullptr) sa = __ldcg(sa_row + kb);
+                    const float wb0 = __ldg(sb0 + kb), wb1 = kSwiGLU ? __ldg(sb1 + kb) : 0.f;
                     if (!mbar_wait(&tmem_full[win], win_phase, abort_flag, limit, note, wait_id(5, tile, kb, warp))) {
                         ok = false;
                         break;
                     }
+                    if (p.ready != nullptr) sa = __ldcg(sa_row + kb);
+                    const float s_lo = sa * wb0, s_hi = kSwiGLU ? sa * wb1 : s_lo;
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(win * kBlockN);
                     uint32_t v[32], u[32];

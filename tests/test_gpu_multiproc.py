@@ -160,11 +160,15 @@ def _worker(rank, world, port, q):
         for native in (False, True):
             layer.prepare_fp8(native_block_scaling=native)
             for rep in range(3):
+                # a different input every time: a value that a kernel picks up from the step before (a scale read before its row
+                # had arrived, a stage row summed before it was written) must show as an error, not repeat the right answer
+                x_rep = (xm.detach() * (0.5 + rep)).contiguous()
+                ref_rep = dense_reference(x_rep, mi, mw, w13_all, w2_all)
                 align()
-                yf = layer.forward_fused(xm.detach(), mi, mw)
+                yf = layer.forward_fused(x_rep, mi, mw)
                 torch.cuda.synchronize()
                 buf.check_status(sync=True)
-                assert rel(yf, ref.detach()) < 8e-2, (native, rep, rel(yf, ref.detach()))
+                assert rel(yf, ref_rep) < 8e-2, (native, rep, rel(yf, ref_rep))
         # ---- a gloo group handed to the rail transport: CUDA tensors travel over a lazily created NCCL twin ----
         from deepep_efa_b200.parallel.transport import CollectiveTransport, group_moves_cuda_tensors
         gloo = dist.new_group(backend="gloo")

@@ -464,28 +464,31 @@ def run_ours(args):
     w_d = stage_d[nx + ni:].view(torch.float32).view_as(topk_w)
     out_p = torch.empty(LL_TOKENS, HIDDEN, dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step():
-        stage_d.copy_(stage_p, non_blocking=True)
-        _, _, h, _, _ = buf.low_latency_dispatch(x_d, idx_d, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
-        buf.low_latency_combine(sim_gemm_out, idx_d, w_d, h, out=out_p)
-
-    def e2e_step_copy_out():
-        # the same step with the result produced in device memory and copied out by the copy engine
-        stage_d.copy_(stage_p, non_blocking=True)
-        _, _, h, _, _ = buf.low_latency_dispatch(x_d, idx_d, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
-        buf.low_latency_combine(sim_gemm_out, idx_d, w_d, h, out=out)
-        out_p.copy_(out, non_blocking=True)
+    def make_e2e(src, store_to_host):
+        def step():
+            stage_d.copy_(stage_p, non_blocking=True)
+            _, _, h, _, _ = buf.low_latency_dispatch(x_d, idx_d, LL_TOKENS, NUM_EXPERTS, use_fp8=True)
+            if store_to_host:
+                buf.low_latency_combine(src, idx_d, w_d, h, out=out_p)   # the combine kernel's stores are the device-to-host transfer
+            else:
+                buf.low_latency_combine(src, idx_d, w_d, h, out=out)
+                out_p.copy_(out, non_blocking=True)                     # result produced on the device, copied out by the copy engine
+        return step
 
     # the host copy of the result must equal what the device path produces
     out_p.zero_()
-    e2e_step()
+    make_e2e(sim_gemm_out, True)()
     ll_step()
     torch.cuda.synchronize()
     assert torch.equal(out_p, out.cpu()), "end-to-end result in pinned host memory differs from the device result"
-    # Which of the two ways of getting the result to the host is faster depends on the machine (where the pinned pages sit
-    # relative to the GPU's PCIe root); both are timed with the full protocol and the faster one is the reported value.
+    # Which way of getting the result to the host is faster depends on the machine (where the pinned pages sit relative to the
+    # GPU's PCIe root) and on where the expert outputs live; every combination is timed with the full protocol and the fastest
+    # one is the reported value.
     e2e_variants = {}
-    for name, fn in (("result_stored_to_pinned_host_by_kernel", e2e_step), ("result_copied_out_by_copy_engine", e2e_step_copy_out)):
+    for name, fn in (("symmetric_expert_output__result_stored_to_pinned_host_by_kernel", make_e2e(sim_gemm_out, True)),
+                     ("symmetric_expert_output__result_copied_out_by_copy_engine", make_e2e(sim_gemm_out, False)),
+                     ("ordinary_expert_output__result_stored_to_pinned_host_by_kernel", make_e2e(sim_gemm_plain, True)),
+                     ("ordinary_expert_output__result_copied_out_by_copy_engine", make_e2e(sim_gemm_plain, False))):
         for _ in range(warmup):
             fn()
         smp = timed_samples(fn, steps, flush)

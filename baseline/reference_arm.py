@@ -117,7 +117,7 @@ def main(args) -> None:
             e2e_step()
         e2e_us = B.max_over_ranks(B.timed_loop(e2e_step, steps, flush) * 1e3)
         result["e2e"] = {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": x_p.numel() * 2 + idx_p.numel() * 8 + w_p.numel() * 4,
-                         "d2h_bytes_per_step": out_p.numel() * 2}
+                         "d2h_bytes_per_step": out_p.numel() * 2, "process_pinned_to_gpu_local_cpus": B.BOUND_CPUS}
     except Exception as e:
         result["e2e"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
 

@@ -151,6 +151,9 @@ class ClockSampler:
         return res
 
 
+BOUND_CPUS = None  # set by init_dist: how many GPU-local CPU cores this process was pinned to (None: not pinned)
+
+
 def physical_gpu_index(local_rank: int) -> int:
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -214,6 +217,26 @@ def ramp_clocks(local_rank: int, max_seconds: float = 12.0) -> None:
 # ------------------------------------------------------------------------------------------------
 # helpers
 # ------------------------------------------------------------------------------------------------
+def bind_to_gpu_local_cpus(local_rank: int):
+    """Pin this process to the CPU cores that NVML reports as local to its GPU (same socket / PCIe root), before any pinned
+    host memory is allocated: the host-to-device and device-to-host copies of the end-to-end number then stay on one NUMA
+    node. Process affinity only (nothing that outlasts the process); best effort, both arms go through it. Returns the
+    number of CPUs bound to, or None when NVML or the cpuset would not allow it."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(local_rank))
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, ((os.cpu_count() or 64) + 63) // 64)
+        local = {i * 64 + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        cpus = local & os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
+
+
 def init_dist(n_gpus: int):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -221,6 +244,8 @@ def init_dist(n_gpus: int):
     assert world == n_gpus, f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n_gpus}"
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
+    global BOUND_CPUS
+    BOUND_CPUS = bind_to_gpu_local_cpus(local_rank)
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
     return rank, world, local_rank
@@ -551,6 +576,7 @@ def run_ours(args):
         "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "median": e2e_spread["median"], "min": e2e_spread["min"],
                 "how": "one packed pinned buffer (x|topk_idx|topk_weights) -> one H2D copy; " + e2e_how.replace("_", " "),
+                "process_pinned_to_gpu_local_cpus": BOUND_CPUS,
                 "variants": e2e_variants},
         "value_median": ll_spread["median"],
         "value_min": ll_spread["min"],

@@ -85,7 +85,8 @@ class RuntimeCore {
         const uint64_t arena_bytes = num_nvl_bytes > kControlBytes ? align_up(num_nvl_bytes - kControlBytes, 1024) : 0;
         total_bytes_ = arena_base + arena_bytes;
         DX_CUDA_CHECK(cudaMalloc(&base_, total_bytes_));
-        DX_CUDA_CHECK(cudaMemset(base_, 0, kControlBytes));
+        // control block, and the low-latency region: its count words carry validity tags and must not start with stale ones
+        DX_CUDA_CHECK(cudaMemset(base_, 0, kControlBytes + ll_bytes_));
         arena_.reset(arena_base, arena_bytes);
         DX_CUDA_CHECK(cudaMalloc(&local_scratch_, kLocalScratchInts * sizeof(int)));
         DX_CUDA_CHECK(cudaMemset(local_scratch_, 0, kLocalScratchInts * sizeof(int)));
@@ -310,7 +311,7 @@ class RuntimeCore {
     void reset_control() {
         DX_CUDA_CHECK(cudaSetDevice(device_));
         DX_CUDA_CHECK(cudaDeviceSynchronize());
-        DX_CUDA_CHECK(cudaMemset(base_, 0, kControlBytes));
+        DX_CUDA_CHECK(cudaMemset(base_, 0, kControlBytes + ll_bytes_));  // sequences restart, so no tagged count word may survive
         DX_CUDA_CHECK(cudaMemset(local_scratch_, 0, kLocalScratchInts * sizeof(int)));
         DX_CUDA_CHECK(cudaMemset(local_seq_, 0, kLocalSeqWords * sizeof(uint64_t)));
         DX_CUDA_CHECK(cudaDeviceSynchronize());

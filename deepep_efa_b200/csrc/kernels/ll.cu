@@ -97,6 +97,22 @@ __device__ __forceinline__ QuantChunk quantize_chunk(const char* row, int ch, bo
 // =============================================================================================
 // The kernels are named dx::ll::dispatch and dx::ll::combine: tools written for the reference and for upstream DeepEP
 // (tests/utils.py:173-271) find the low-latency kernels in a profiler trace by the substrings "::dispatch" / "::combine".
+// A count word carries its own validity tag, (tag << 16) | count with tag = (sequence mod 65535) + 1, so the sender needs no
+// release behind the counts and a receiver polls exactly the words it uses. A parity's matrix is rewritten every second call, so a
+// stale word never carries the current tag; the matrices start zeroed (tag 0 is never used).
+__device__ __forceinline__ int ll_count_tag(uint64_t seq) { return (int)(seq % 65535ull) + 1; }
+
+// Bounded poll of one count word: the count, or -1 when the limit ran out.
+__device__ __forceinline__ int wait_tagged_count(const int* p, int tag, long long limit) {
+    unsigned w = (unsigned)ld_relaxed_sys(p);
+    if ((w >> 16) == (unsigned)tag) return (int)(w & 0xffffu);
+    const long long t0 = clock64();
+    while (((w = (unsigned)ld_relaxed_sys(p)) >> 16) != (unsigned)tag) {
+        if (clock64() - t0 > limit) return -1;
+    }
+    return (int)(w & 0xffffu);
+}
+
 namespace ll {
 template <int V>
 __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant__ ArgPack<LLDispatchArgs, V> pack) {
@@ -125,6 +141,8 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
     __shared__ int s_dst_le[kMaxTopk];
     __shared__ int s_sent[kMaxRanks];
     __shared__ int s_expected[kMaxRanks];
+    __shared__ int s_cnt[kMaxTopk][kMaxRanks];  // counts of the ranks before me for the experts of the current token
+    const int count_tag = ll_count_tag(seq);
 
     const int tslot = is_tail_cta ? 1 : 0;
     const bool traced = is_tail_cta || blockIdx.x == 0;
@@ -149,22 +167,22 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
         for (int i = tid; i < T * K; i += kLLThreads)
             if (s_idx[i] >= 0) atomicAdd(&s_hist[s_idx[i]], 1);
         __syncthreads();
+        const int tagw = count_tag << 16;
         if ((E & 3) == 0) {
             const int e4 = E / 4;
             for (int i = tid; i < e4 * R; i += kLLThreads) {
                 const int d = i / e4, j = i % e4;
                 if (s_mask[d]) continue;
-                const int4 v = make_int4(s_hist[4 * j], s_hist[4 * j + 1], s_hist[4 * j + 2], s_hist[4 * j + 3]);
+                const int4 v = make_int4(tagw | s_hist[4 * j], tagw | s_hist[4 * j + 1], tagw | s_hist[4 * j + 2], tagw | s_hist[4 * j + 3]);
                 *(reinterpret_cast<int4*>(c.at<int>(d, a.region.counts_off[P]) + (size_t)me * E) + j) = v;
             }
         } else {
             for (int i = tid; i < E * R; i += kLLThreads) {
                 const int d = i / E, e = i % E;
-                if (!s_mask[d]) c.at<int>(d, a.region.counts_off[P])[(size_t)me * E + e] = s_hist[e];
+                if (!s_mask[d]) c.at<int>(d, a.region.counts_off[P])[(size_t)me * E + e] = tagw | s_hist[e];
             }
         }
-        __syncthreads();
-        if (tid < R && !s_mask[tid]) st_release_sys(&c.ctrl(tid)->ll_count_seq[P][me], seq);
+        // no release: every word says for itself whether it belongs to this call
         trace_stamp(c, kFamLLDispatch, 1, 2);
     }
 
@@ -198,20 +216,29 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
                 s_dst_rank[tid] = e >= 0 ? e / L : 0;
                 s_dst_le[tid] = e >= 0 ? e % L : 0;
             }
-            // counts of the ranks before me decide where my segment starts
-            if (!counts_known && tid < me && !s_mask[tid]) {
-                const long long t0 = clock64();
-                if (!wait_ge_sys(&my->ll_count_seq[P][tid], seq, c.timeout_cycles)) {
-                    report(c.status, kTimeoutLLCount, me, tid, 0);
-                    if (c.mask_on_timeout) {
-                        // shrink mode: a silent rank sends nothing to anybody, so every sender drops its counts alike
-                        st_relaxed_sys(&my->ll_mask[tid], 1);
-                        s_mask[tid] = 1;
-                    } else {
-                        s_ok = 0;
+            __syncthreads();
+            // counts of the ranks before me decide where my segment starts: one thread per (selection, lower rank) polls its word
+            for (int i = tid; i < K * me; i += kLLThreads) {
+                const int k = i / me, src = i % me;
+                int cnt = 0;
+                if (s_row[k] >= 0 && !s_mask[src]) {
+                    const long long t0 = clock64();
+                    cnt = wait_tagged_count(&my_counts[(size_t)src * E + s_dst_rank[k] * L + s_dst_le[k]], count_tag, c.timeout_cycles);
+                    if (cnt < 0) {
+                        cnt = 0;
+                        report(c.status, kTimeoutLLCount, me, src, 0);
+                        if (c.mask_on_timeout) {
+                            // shrink mode: a silent rank sends nothing to anybody, so every sender drops its counts alike
+                            st_relaxed_sys(&my->ll_mask[src], 1);
+                            s_mask[src] = 1;
+                        } else {
+                            s_ok = 0;
+                        }
                     }
+                    if (a.wait_cost_stats != nullptr && blockIdx.x == 0 && k == 0 && !counts_known)
+                        atomicAdd((unsigned long long*)&a.wait_cost_stats[src], (unsigned long long)(clock64() - t0));
                 }
-                if (a.wait_cost_stats != nullptr && blockIdx.x == 0) atomicAdd((unsigned long long*)&a.wait_cost_stats[tid], (unsigned long long)(clock64() - t0));
+                s_cnt[k][src] = cnt;
             }
             counts_known = true;
             __syncthreads();
@@ -223,7 +250,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
                     const int e = s_dst_rank[tid] * L + s_dst_le[tid];
                     int begin = 0;
                     for (int src = 0; src < me; ++src)
-                        if (!s_mask[src]) begin += __ldcg(&my_counts[(size_t)src * E + e]);
+                        if (!s_mask[src]) begin += s_cnt[tid][src];
                     const int row = begin + s_row[tid];
                     const size_t row_bytes = (size_t)H * (a.use_fp8 ? 1 : 2);
                     if (row >= N || s_mask[s_dst_rank[tid]] ||
@@ -286,18 +313,26 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
 
     if (do_recv && is_tail_cta) {
         // ---- receive side: counts -> layout, then wait for the rows ----
-        if (tid < R && !s_mask[tid]) {
-            const long long t0 = clock64();
-            if (!wait_ge_sys(&my->ll_count_seq[P][tid], seq, c.timeout_cycles)) {
-                report(c.status, kTimeoutLLCount, me, tid, 1);
-                if (c.mask_on_timeout) {
-                    st_relaxed_sys(&my->ll_mask[tid], 1);
-                    s_mask[tid] = 1;
-                } else {
-                    s_ok = 0;
+        __syncthreads();  // the send part is done with s_hist: from here on it holds the counts received, [R][L]
+        for (int i = tid; i < R * L; i += kLLThreads) {
+            const int src = i / L, le = i % L;
+            int cnt = 0;
+            if (!s_mask[src]) {
+                const long long t0 = clock64();
+                cnt = wait_tagged_count(&my_counts[(size_t)src * E + me * L + le], count_tag, c.timeout_cycles);
+                if (cnt < 0) {
+                    cnt = 0;
+                    report(c.status, kTimeoutLLCount, me, src, 1);
+                    if (c.mask_on_timeout) {
+                        st_relaxed_sys(&my->ll_mask[src], 1);
+                        s_mask[src] = 1;
+                    } else {
+                        s_ok = 0;
+                    }
                 }
+                if (a.wait_cost_stats != nullptr && le == 0) atomicAdd((unsigned long long*)&a.wait_cost_stats[src], (unsigned long long)(clock64() - t0));
             }
-            if (a.wait_cost_stats != nullptr) atomicAdd((unsigned long long*)&a.wait_cost_stats[tid], (unsigned long long)(clock64() - t0));
+            s_hist[i] = cnt;
         }
         __syncthreads();
         trace_stamp(c, kFamLLDispatch, 1, 3);
@@ -305,7 +340,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
         for (int le = tid; counts_ok && le < L; le += kLLThreads) {
             int run = 0;
             for (int src = 0; src < R; ++src) {
-                const int cnt = s_mask[src] ? 0 : __ldcg(&my_counts[(size_t)src * E + me * L + le]);
+                const int cnt = s_mask[src] ? 0 : s_hist[src * L + le];
                 a.layout_range[(size_t)le * R + src] = ((int64_t)run << 32) | (int64_t)cnt;
                 run += cnt;
             }
@@ -316,7 +351,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
         for (int src = warp; counts_ok && src < R; src += kLLWarps) {
             int sum = 0;
             if (!s_mask[src])
-                for (int le = lane; le < L; le += 32) sum += __ldcg(&my_counts[(size_t)src * E + me * L + le]);
+                for (int le = lane; le < L; le += 32) sum += s_hist[src * L + le];
             sum = warp_sum(sum);
             if (lane == 0) s_expected[src] = sum;
         }

@@ -332,6 +332,10 @@ class Buffer:
             dist.barrier(self.group)
         self.runtime.reset_control()
         self._ll_parity = 0
+        for views in self._ll_cache.values():  # sequences restart: no row-number word may keep a tag of the old numbering
+            for v in views:
+                v["send_row"].zero_()
+        torch.cuda.synchronize()
         if self.group is not None and self.group_size > 1:
             dist.barrier(self.group)
 
@@ -480,7 +484,8 @@ class Buffer:
                 layout_range=torch.zeros(L, R, dtype=torch.int64, device=self.device),
                 # row of every (token, k) selection at its expert's rank, written by dispatch and read by the pull form of
                 # combine; lives as long as the handle's tensors (until the second next dispatch)
-                send_row=torch.full((num_max_tokens * 32,), -1, dtype=torch.int32, device=self.device),
+                # (words are (call tag << 16) | (row + 1); zero = never written)
+                send_row=torch.zeros(num_max_tokens * 32, dtype=torch.int32, device=self.device),
             )
             v.append(d)
         self._ll_cache[key] = v

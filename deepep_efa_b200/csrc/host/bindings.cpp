@@ -466,6 +466,7 @@ void ll_dispatch(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int
         const int T = (int)x.size(0), H = (int)x.size(1);
         DX_CHECK(T <= num_max_tokens, "more tokens than num_max_dispatch_tokens_per_rank");
         DX_CHECK(num_max_tokens <= 65535, "num_max_dispatch_tokens_per_rank must fit the 16-bit count field of the count exchange");
+        DX_CHECK((int64_t)R * num_max_tokens < 65535, "rows per expert (ranks x num_max_dispatch_tokens_per_rank) must fit the 16-bit row field of send_row");
         DX_CHECK(H % 128 == 0 && (!use_ue8m0 || H % 512 == 0), "hidden must be a multiple of 128 (512 with UE8M0)");
         DX_CHECK(topk_idx.scalar_type() == torch::kInt64 && topk_idx.is_contiguous() && topk_idx.dim() == 2 && topk_idx.size(0) == T, "topk_idx must be int64 [T,K]");
         DX_CHECK(topk_idx.size(1) <= dx::kMaxTopk, "num_topk too large");

@@ -69,7 +69,7 @@ struct HostWords {
 
 constexpr int kLocalScratchInts = 64;
 // sequences + low-latency expected arrivals + expected rows per local expert of the expert-major dispatch
-constexpr int kLocalSeqWords = dx::kFusedExpectedWord0 + dx::kMaxLocalExperts;
+constexpr int kLocalSeqWords = dx::kLLStartedWord0 + 2;
 
 class RuntimeCore {
   public:

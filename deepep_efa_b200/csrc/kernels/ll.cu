@@ -117,7 +117,6 @@ namespace ll {
 template <int V>
 __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant__ ArgPack<LLDispatchArgs, V> pack) {
     pdl_wait_predecessor();
-    pdl_release_successor();
     const LLDispatchArgs& a = pack.a[blockIdx.y];
     const RankCtx& c = a.ctx;
     const int R = c.num_ranks, me = c.rank, T = a.num_tokens, K = a.num_topk, E = a.num_experts;
@@ -144,6 +143,15 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
     __shared__ int s_cnt[kMaxTopk][kMaxRanks];  // counts of the ranks before me for the experts of the current token
     const int count_tag = ll_count_tag(seq);
 
+    // Which call last used this parity: a combine that the stream lets start while this kernel still waits for its last rows
+    // (programmatic dependent launch) learns from it that its dispatch is in flight, and what tag the row numbers carry.
+    // Written (and fenced) before this CTA allows the successor's launch, so no successor CTA can run before it is in memory.
+    if (do_send && blockIdx.x == 0 && tid == 0) {
+        *reinterpret_cast<volatile uint64_t*>(c.seq + kLLStartedWord0 + P) = seq;
+        __threadfence();
+    }
+    __syncthreads();
+    pdl_release_successor();
     const int tslot = is_tail_cta ? 1 : 0;
     const bool traced = is_tail_cta || blockIdx.x == 0;
     if (traced) trace_stamp(c, kFamLLDispatch, tslot, 0);
@@ -263,7 +271,8 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch(const __grid_constant_
                     }
                 }
                 // where this selection landed at its expert's rank: the pull form of combine reads the output row back from there
-                if (a.send_row != nullptr) a.send_row[t * K + tid] = final_row;
+                // (tagged like the count words: a combine that overlaps this kernel polls the word until it is this call's)
+                if (a.send_row != nullptr) a.send_row[t * K + tid] = (count_tag << 16) | (final_row + 1);
             }
             __syncthreads();
             if (traced) trace_stamp(c, kFamLLDispatch, 0, 3);
@@ -596,7 +605,6 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine(const __grid_constant__
 // (expert rank, home rank): "outputs final, at this offset".
 template <int V>
 __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_constant__ ArgPack<LLCombineArgs, V> pack) {
-    pdl_wait_predecessor();
     pdl_release_successor();
     const LLCombineArgs& a = pack.a[blockIdx.y];
     const RankCtx& c = a.ctx;
@@ -605,6 +613,30 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_const
     const int N = R * a.num_max_tokens;
     const int n16 = H / 8;
     const int tid = threadIdx.x;
+    // When this kernel directly follows the dispatch of its handle, programmatic dependent launch lets its CTAs start while
+    // that dispatch still waits for the last rows of the other ranks. Nothing this kernel reads depends on those rows: the
+    // expert outputs were final before the dispatch began, and the row numbers it needs are written early by the dispatch's
+    // token CTAs, each word tagged with the call it belongs to. So a CTA that finds its dispatch still in flight (started, not
+    // yet committed) does its work first and waits for the predecessor only before it exits, which keeps the stream's order of
+    // completion. In every other case (dispatch already complete: an expert GEMM ran in between, or the launch is an ordinary
+    // one) the wait comes first, as for any dependent kernel. A stale read of either word can only choose the second way.
+    __shared__ int s_early;
+    __shared__ unsigned long long s_seq_d;
+    if (tid == 0) {
+        const uint64_t started = *reinterpret_cast<volatile uint64_t*>(c.seq + kLLStartedWord0 + a.parity);
+        const uint64_t committed = *reinterpret_cast<volatile uint64_t*>(c.seq + kFamLLDispatch);
+        s_early = committed < started ? 1 : 0;
+        s_seq_d = started;
+    }
+    __syncthreads();
+    const bool early = s_early != 0;
+    if (!early) {
+        pdl_wait_predecessor();
+        __syncthreads();
+        if (tid == 0) s_seq_d = *reinterpret_cast<volatile uint64_t*>(c.seq + kLLStartedWord0 + a.parity);
+        __syncthreads();
+    }
+    const int row_tag = ll_count_tag(s_seq_d);
     const uint64_t seq = next_seq(c, kFamLLCombine);
     const bool do_send = a.phases & 1, do_recv = a.phases & 2;
     ControlBlock* my = c.my_ctrl();
@@ -652,7 +684,19 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_const
                 __syncthreads();
                 if (tid < K) {
                     const int64_t e = a.topk_idx[(size_t)t * K + tid];
-                    const int row = a.send_row[(size_t)t * K + tid];
+                    // the word is (tag << 16) | (row + 1); while the dispatch is still running it may not have been written yet
+                    unsigned wrow = (unsigned)ld_relaxed_sys(a.send_row + (size_t)t * K + tid);
+                    if ((wrow >> 16) != (unsigned)row_tag) {
+                        const long long t0 = clock64();
+                        while (((wrow = (unsigned)ld_relaxed_sys(a.send_row + (size_t)t * K + tid)) >> 16) != (unsigned)row_tag) {
+                            if (clock64() - t0 > c.timeout_cycles) {
+                                report(c.status, kTimeoutCombineReady, me, me, 2);
+                                wrow = 0;
+                                break;
+                            }
+                        }
+                    }
+                    const int row = (int)(wrow & 0xffffu) - 1;
                     bool ok = e >= 0 && e < E && row >= 0 && row < N && !s_mask[(int)e / L];
                     const int r = ok ? (int)e / L : 0;
                     const long long off = ok ? ((long long)((int)e % L) * N + row) * n16 : -1;
@@ -721,6 +765,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_const
         }
         if (traced) trace_stamp(c, kFamLLCombine, tslot, 6);
     }
+    if (early) pdl_wait_predecessor();  // this kernel may not complete before its predecessor has
 }
 
 }  // namespace ll

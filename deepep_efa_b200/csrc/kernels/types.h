@@ -119,5 +119,7 @@ constexpr int kTraceStampsPerSlot = 16;  // trace layout: [family][slot 0 = firs
 
 enum Family : int { kFamNotify = 0, kFamDispatch = 1, kFamCombine = 2, kFamBarrier = 3, kFamLLDispatch = 4, kFamLLCombine = 5, kFamFused = 6, kNumFamilies = 8 };
 static_assert(kFusedExpectedWord0 == kNumFamilies + 2 * 2 * kMaxRanks, "layout of the rank-local sequence words");
+// after the fused layer's expected-arrival words: per parity, the sequence number of the low-latency dispatch that last used it
+constexpr int kLLStartedWord0 = kFusedExpectedWord0 + kMaxLocalExperts;
 
 }  // namespace dx

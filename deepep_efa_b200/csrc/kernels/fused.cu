@@ -25,7 +25,9 @@
 
 namespace dx {
 
-constexpr int kEmNotifyThreads = 512;
+// One warp per expert scans all selections, so the scan's length is fixed; what varies is how many such warps share an SM's four
+// schedulers. Four warps per CTA (64 CTAs for 256 experts) give every scanning warp a scheduler of its own.
+constexpr int kEmNotifyThreads = 128;
 constexpr int kEmNotifyWarps = kEmNotifyThreads / 32;
 constexpr int kEmChunk = 16384;          // selections staged in shared memory per pass (uint16 expert ids)
 constexpr int kTicketFused = 5;
@@ -49,9 +51,23 @@ __global__ void __launch_bounds__(kEmNotifyThreads, 1) em_notify_kernel(const __
     for (int c0 = 0; c0 < TK; c0 += kEmChunk) {
         const int n = min(kEmChunk, TK - c0);
         __syncthreads();
-        for (int i = tid; i < n; i += kEmNotifyThreads) {
-            const int64_t v = a.topk_idx[c0 + i];
-            s_sel[i] = (v >= 0 && v < E) ? (uint16_t)v : (uint16_t)0xFFFF;
+        if (((reinterpret_cast<uintptr_t>(a.topk_idx + c0)) & 15) == 0) {
+            // two ids per 16-byte load
+            const longlong2* src2 = reinterpret_cast<const longlong2*>(a.topk_idx + c0);
+            for (int i = tid; i < n / 2; i += kEmNotifyThreads) {
+                const longlong2 v = src2[i];
+                const uint32_t lo = (v.x >= 0 && v.x < E) ? (uint32_t)v.x : 0xFFFFu, hi = (v.y >= 0 && v.y < E) ? (uint32_t)v.y : 0xFFFFu;
+                reinterpret_cast<uint32_t*>(s_sel)[i] = lo | (hi << 16);
+            }
+            if ((n & 1) && tid == 0) {
+                const int64_t v = a.topk_idx[c0 + n - 1];
+                s_sel[n - 1] = (v >= 0 && v < E) ? (uint16_t)v : (uint16_t)0xFFFF;
+            }
+        } else {
+            for (int i = tid; i < n; i += kEmNotifyThreads) {
+                const int64_t v = a.topk_idx[c0 + i];
+                s_sel[i] = (v >= 0 && v < E) ? (uint16_t)v : (uint16_t)0xFFFF;
+            }
         }
         __syncthreads();
         if (e < E) {

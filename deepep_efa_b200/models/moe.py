@@ -312,7 +312,7 @@ FUSE_CAST_INTO_GEMM1 = True  # wide natively block-scaled tiles: GEMM1's epilogu
 RESERVED_SMS = 16
 # The gated GEMM runs as two launches when it overlaps the dispatch: the first part of the experts (arrival order = expert
 # order) on the SMs the dispatch does not use, the rest on all SMs once the dispatch is about done.
-SPLIT_FRACTION = 0.35
+SPLIT_FRACTION = 0.5
 PREQUANTIZE = True  # cast every token to e4m3 once before the dispatch, which then only copies rows (8 selections share a cast)
 GEMM_TIMEOUT_MS = 2000.0  # bound of every wait inside the gated GEMMs (pipeline barriers and arrival counters)
 
@@ -393,16 +393,23 @@ def fused_forward_many(layers, xs, idxs, ws, overlap: bool = True, num_dispatch_
     native = wss[0].native
     cur = torch.cuda.current_stream()
     comm = bufs[0].comm_stream if (V == 1 and overlap) else cur
+    if comm is not cur:
+        comm.wait_stream(cur)
+    # the quantisation of x (caller's stream) and the count exchange (communication stream) do not depend on each other: side by side
+    quantised = None
     if PREQUANTIZE:
         for x, w in zip(xs, wss):
             C.per_token_cast_to_fp8(x, native, False, None, 1, w.xq, w.xs)
-    if comm is not cur:
-        comm.wait_stream(cur)
+        if comm is not cur:
+            quantised = torch.cuda.Event()
+            quantised.record(cur)
     with torch.cuda.stream(comm):
         C.em_notify(rts, [(i, w.recv_x, w.recv_scales_raw, w.recv_info, w.stage, w.my_counts, w.sel_list, w.send_base, w.unit_start,
                            w.m_offsets, w.m_ends, w.peer_bases) for i, w in zip(idxs, wss)], E, UNIT_ROWS)
         planned = torch.cuda.Event()
         planned.record(comm)
+        if quantised is not None:
+            comm.wait_event(quantised)
         sms = num_dispatch_sms or (148 if V == 1 else max(1, 148 // V - 1))
         C.em_dispatch(rts, [(w.xq if PREQUANTIZE else x, w.my_counts, w.sel_list, w.send_base, w.unit_start, w.peer_bases, None,
                              None if w.trace is None else w.trace[0:2], w.xs if PREQUANTIZE else None) for x, w in zip(xs, wss)],

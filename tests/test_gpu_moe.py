@@ -71,7 +71,8 @@ def test_moe_layer_forward_backward_gpu():
         # routing through the layer's own gate
         y2 = layer(x.detach())
         assert y2.shape == (T, H) and torch.isfinite(y2.float()).all()
-        # FP8 forward path
+        # FP8 forward path with arbitrary fp32 block scales (promoted on the CUDA cores)
+        layer.prepare_fp8(native_block_scaling=False)
         y8 = layer.forward_fp8(x.detach(), idx, w.detach())
         torch.cuda.synchronize()
         buf.check_status()
@@ -99,6 +100,7 @@ def test_moe_low_latency_decode_path():
         x = make_tokens(T, H, "cuda", seed=5)
         idx, w = make_routing(T, E, K, "cuda", seed=5, masked_fraction=0.1)
         ref = dense_reference(x, idx, w.masked_fill(idx == -1, 0), layer.w13.detach().float(), layer.w2.detach().float())
+        layer.prepare_fp8(native_block_scaling=False)
         for _ in range(3):  # both parities, workspace reuse
             y = layer.forward_low_latency(x, idx, w, num_max_tokens=64)
             torch.cuda.synchronize()

@@ -147,6 +147,7 @@ def _worker(rank, world, port, q):
         assert rel(ym, ref) < 3e-2, rel(ym, ref)
         assert rel(xm.grad, xr.grad) < 6e-2, rel(xm.grad, xr.grad)
         align()
+        layer.prepare_fp8(native_block_scaling=False)
         y8 = layer.forward_fp8(xm.detach(), mi, mw)
         torch.cuda.synchronize()
         buf.check_status()

@@ -41,6 +41,13 @@ def _worker(rank, world, port, q):
         topk_w = topk_w.masked_fill(topk_idx == -1, 0)
         buf = ep.Buffer(dist.group.WORLD, num_nvl_bytes=1 << 20, num_nvl_ranks=P)
         assert buf.get_num_rdma_ranks() == nodes and buf.get_rdma_rank() == rank // P
+        # a gloo group serves CPU tensors as it is; only a CUDA tensor would make the transport create its NCCL twin
+        from deepep_efa_b200.parallel.transport import CollectiveTransport, group_moves_cuda_tensors
+        assert not group_moves_cuda_tensors(dist.group.WORLD)
+        tr = CollectiveTransport(dist.group.WORLD)
+        assert tr.group_for(torch.zeros(1)) is dist.group.WORLD and tr._gpu_group is None
+        got = tr.all_to_all_equal(torch.full((world * 2, 3), float(rank)))
+        assert torch.equal(got[:, 0], torch.arange(world, dtype=got.dtype).repeat_interleave(2))
 
         # ---- layout
         per_rank, per_node, per_expert, in_rank, _ = buf.get_dispatch_layout(topk_idx, E)

@@ -858,7 +858,7 @@ def _ll_stream_exit(buf: Buffer, ctx, tensors) -> EventOverlap:
         return EventOverlap()
     ctx.__exit__(None, None, None)
     for t in tensors:
-        if isinstance(t, torch.Tensor) and buf.runtime.symmetric_offset(t) < 0:
+        if isinstance(t, torch.Tensor) and t.is_cuda and buf.runtime.symmetric_offset(t) < 0:
             t.record_stream(buf.comm_stream)
     return EventOverlap(EventHandle(buf.comm_stream))
 

@@ -460,9 +460,14 @@ void ll_dispatch(std::vector<Runtime*> rts, std::vector<py::tuple> per_rank, int
         auto wait = opt_tensor(t[5]);
         auto slot = opt_tensor(t[6]);
         const int R = rt->core->num_ranks();
-        DX_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "x must be contiguous bf16 [T,hidden] on the GPU");
-        DX_CHECK(x.device().index() == rt->core->device() && topk_idx.is_cuda() && topk_idx.device() == x.device() && count.is_cuda() && range.is_cuda(),
-                 "low_latency_dispatch: every tensor must live on this rank's GPU");
+        // x may also sit in pinned host memory: the token CTAs then read their rows over PCIe themselves (each row is read
+        // exactly once), which is the host-to-device transfer without a copy in front of the kernel
+        const bool x_on_gpu = x.is_cuda() && x.device().index() == rt->core->device();
+        const bool x_pinned = x.device().is_cpu() && x.is_pinned();
+        DX_CHECK((x_on_gpu || x_pinned) && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16,
+                 "x must be contiguous bf16 [T,hidden] on this rank's GPU or in pinned host memory");
+        DX_CHECK(topk_idx.is_cuda() && topk_idx.device().index() == rt->core->device() && count.is_cuda() && range.is_cuda(),
+                 "low_latency_dispatch: every tensor but x must live on this rank's GPU");
         const int T = (int)x.size(0), H = (int)x.size(1);
         DX_CHECK(T <= num_max_tokens, "more tokens than num_max_dispatch_tokens_per_rank");
         DX_CHECK(num_max_tokens <= 65535, "num_max_dispatch_tokens_per_rank must fit the 16-bit count field of the count exchange");

@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(kEmNotifyThreads, 1) em_notify_kernel(const __
         if (((reinterpret_cast<uintptr_t>(a.topk_idx + c0)) & 15) == 0) {
             // two ids per 16-byte load
             const longlong2* src2 = reinterpret_cast<const longlong2*>(a.topk_idx + c0);
+#pragma unroll 8
             for (int i = tid; i < n / 2; i += kEmNotifyThreads) {
                 const longlong2 v = src2[i];
                 const uint32_t lo = (v.x >= 0 && v.x < E) ? (uint32_t)v.x : 0xFFFFu, hi = (v.y >= 0 && v.y < E) ? (uint32_t)v.y : 0xFFFFu;
@@ -71,15 +72,25 @@ __global__ void __launch_bounds__(kEmNotifyThreads, 1) em_notify_kernel(const __
         }
         __syncthreads();
         if (e < E) {
-            for (int i0 = 0; i0 < n; i0 += 32) {
-                const int i = i0 + lane;
-                const bool hit = i < n && s_sel[i] == (uint16_t)e;
-                const unsigned b = __ballot_sync(0xffffffffu, hit);
-                if (hit) {
-                    const int slot = run + __popc(b & ((1u << lane) - 1));
-                    if (slot < T) a.sel_list[(size_t)e * T + slot] = c0 + i;  // an expert is selected at most once per token
+            // four groups of 32 selections per step, so that four shared-memory loads and votes are in flight at a time
+            for (int i0 = 0; i0 < n; i0 += 128) {
+                bool hit[4];
+                unsigned b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * 32 + lane;
+                    hit[u] = i < n && s_sel[i] == (uint16_t)e;
                 }
-                run += __popc(b);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) b[u] = __ballot_sync(0xffffffffu, hit[u]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (hit[u]) {
+                        const int slot = run + __popc(b[u] & ((1u << lane) - 1));
+                        if (slot < T) a.sel_list[(size_t)e * T + slot] = c0 + i0 + u * 32 + lane;  // an expert is selected at most once per token
+                    }
+                    run += __popc(b[u]);
+                }
             }
         }
     }

@@ -168,6 +168,20 @@ def test_ll_pull_equals_push_host_out_and_sm_knob(R, T, H, E, K, num_sms):
             assert oracle.calc_diff(want, push[r].float()) < 2e-5
             assert torch.equal(push[r], pull[r])
             assert torch.equal(push[r].cpu(), host[r])
+        # activations in pinned host memory: the dispatch kernel reads the rows over PCIe itself, same bits
+        first = [((r_[0][0].clone(), r_[0][1].clone()), r_[1].clone(), r_[2][0].clone()) for r_ in vc.low_latency_dispatch(xs, idxs, T, E, use_fp8=True)]
+        pinned = [x.cpu().pin_memory() for x in xs]
+        again = vc.low_latency_dispatch(pinned, idxs, T, E, use_fp8=True)
+        torch.cuda.synchronize()
+        for b in vc.buffers:
+            b.check_status()
+        for r in range(R):
+            assert torch.equal(first[r][1], again[r][1])
+            for le in range(L):
+                n = int(first[r][1][le])
+                assert torch.equal(first[r][2][le, :n], again[r][2][0][le, :n])
+                assert torch.equal(first[r][0][0][le, :n].view(torch.uint8), again[r][0][0][le, :n].view(torch.uint8))
+                assert torch.equal(first[r][0][1][le, :n], again[r][0][1][le, :n])
     finally:
         Buffer.set_low_latency_num_sms(None)
         vc.destroy()

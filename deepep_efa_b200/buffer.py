@@ -660,10 +660,19 @@ class _CommScope:
         self.buf, self.prev, self.async_finish = buf, previous_event, async_finish
         self.inputs = [t for t in inputs if isinstance(t, torch.Tensor)]
         self._outputs: List[torch.Tensor] = []
+        self._early_outputs: List[torch.Tensor] = []
         self.event = EventOverlap()
 
     def outputs(self, *tensors):
         self._outputs.extend(t for t in tensors if isinstance(t, torch.Tensor))
+
+    def outputs_from_caller_stream(self, *tensors):
+        """Outputs that were allocated BEFORE the block, on the caller's stream. Without ``async_finish`` the caller's stream
+        waits for the communication stream on exit, so such a block needs no ``record_stream`` at all: freed on the caller's
+        stream it is reusable at once. (A block allocated under the communication stream and recorded on the caller's stream is
+        reusable only after an event, and a host that runs ahead of the GPU then makes the caching allocator ``cudaMalloc`` a
+        fresh block on every call: a combine of 4096 x 7168 was measured at 1.4 ms instead of 0.28 ms that way.)"""
+        self._early_outputs.extend(t for t in tensors if isinstance(t, torch.Tensor))
 
     def __enter__(self):
         self.compute = torch.cuda.current_stream()
@@ -686,8 +695,9 @@ class _CommScope:
             if t.is_cuda and self.buf.runtime.symmetric_offset(t) < 0:
                 t.record_stream(self.compute)
         if self.async_finish:
-            for t in self.inputs:
-                t.record_stream(comm)
+            for t in self.inputs + self._early_outputs:
+                if t.is_cuda:
+                    t.record_stream(comm)
             self.event = EventOverlap(EventHandle(comm), tuple(self.inputs))
         else:
             self.compute.wait_stream(comm)
@@ -810,8 +820,15 @@ def _combine_many(bufs: List[Buffer], calls, config: Config, previous_event, asy
     for x, handle, w, bias in calls:
         inputs += [x, w] + list(Buffer._unpack_bias(bias))
     results, per_rank, keep = [], [], []
+    # results are allocated here, on the caller's stream (see _CommScope.outputs_from_caller_stream)
+    early = []
+    if not allocate_on_comm_stream:
+        for x, handle, w, bias in calls:
+            T = handle[5].size(0)
+            early.append((torch.empty((T, x.size(1)), dtype=torch.bfloat16, device=x.device),
+                          torch.empty((T, w.size(1)), dtype=torch.float32, device=x.device) if w is not None else None))
     with _CommScope(bufs[0], previous_event, async_finish, allocate_on_comm_stream, inputs) as scope, nvtx_range("ep.combine"):
-        for b, (x, handle, w, bias) in zip(bufs, calls):
+        for ci, (b, (x, handle, w, bias)) in enumerate(zip(bufs, calls)):
             rpm, _, _, src_idx, _, send_head = handle
             if _DEBUG_CHECKS:
                 validate_handle(handle, b.rank, b.group_size)
@@ -828,10 +845,14 @@ def _combine_many(bufs: List[Buffer], calls, config: Config, previous_event, asy
             keep += [x, w]
             b0, b1 = Buffer._unpack_bias(bias)
             T = send_head.size(0)
-            out = torch.empty((T, x.size(1)), dtype=torch.bfloat16, device=x.device)
-            out_w = torch.empty((T, w.size(1)), dtype=torch.float32, device=x.device) if w is not None else None
+            if early:
+                out, out_w = early[ci]
+                scope.outputs_from_caller_stream(out, out_w)
+            else:
+                out = torch.empty((T, x.size(1)), dtype=torch.bfloat16, device=x.device)
+                out_w = torch.empty((T, w.size(1)), dtype=torch.float32, device=x.device) if w is not None else None
+                scope.outputs(out, out_w)
             per_rank.append((x, w, send_head, rpm, b0, b1, out, out_w))
-            scope.outputs(out, out_w)
             results.append([out, out_w])
         C.combine(rts, per_rank, num_sms)
     del keep

@@ -73,8 +73,7 @@ struct alignas(128) ControlBlock {
     int notify_rank_counts[kMaxRanks][kMaxRanks];          // source's whole num_tokens_per_rank[]
     int notify_expert_counts[kMaxRanks][kMaxLocalExperts]; // source's counts for MY local experts
     int chan_prefix_in[kMaxRanks][kMaxChannels];           // source's per-channel prefix towards me
-    // low-latency mode, two parities
-    uint64_t ll_count_seq[2][kMaxRanks];
+    // low-latency mode, two parities (the count exchange needs no flag here: its words carry their own validity tag)
     uint64_t ll_data_arrived[2][kMaxRanks];                // monotonically growing row counters
     uint64_t ll_combine_arrived[2][kMaxRanks];
     int ll_mask[kMaxRanks];                                // 1 = rank is masked out (shrink mode)

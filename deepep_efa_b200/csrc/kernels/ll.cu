@@ -655,8 +655,8 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_const
 
     if (do_send && blockIdx.x == 0 && tid < R && !s_mask[tid]) {
         // the kernel that produced x is complete (stream order), so its writes are in this GPU's memory system
-        const uint64_t w[1] = {a.x_off};
-        mailbox_post(c, kMbLLCombine, tid, w, 1, seq);
+        // one self-validating word per peer: no payload-then-flag pair, so no release round trip in front of the peers' loads
+        st_relaxed_sys(&c.ctrl(tid)->ll_pull_src[seq & 1][me], ((seq & 0xffffffull) << 40) | (a.x_off & ((1ull << 40) - 1)));
     }
     if (traced) trace_stamp(c, kFamLLCombine, tslot, 1);
 
@@ -664,7 +664,15 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_const
         if (tid < R && !s_mask[tid]) {
             uint64_t w[1];
             const long long t0 = clock64();
-            if (!mailbox_wait(c, kMbLLCombine, tid, seq, w, 1)) {
+            bool got = true;
+            while (((w[0] = ld_relaxed_sys(&my->ll_pull_src[seq & 1][tid])) >> 40) != (seq & 0xffffffull)) {
+                if (clock64() - t0 > c.timeout_cycles) {
+                    got = false;
+                    break;
+                }
+            }
+            w[0] &= (1ull << 40) - 1;
+            if (!got) {
                 report(c.status, kTimeoutCombineReady, me, tid, 1);
                 if (c.mask_on_timeout) {
                     st_relaxed_sys(&my->ll_mask[tid], 1);

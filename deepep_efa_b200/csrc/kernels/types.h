@@ -77,6 +77,11 @@ struct alignas(128) ControlBlock {
     uint64_t ll_data_arrived[2][kMaxRanks];                // monotonically growing row counters
     uint64_t ll_combine_arrived[2][kMaxRanks];
     int ll_mask[kMaxRanks];                                // 1 = rank is masked out (shrink mode)
+    // pull combine: rank r tells me where its expert outputs lie, (call tag << 40) | byte offset in its symmetric buffer.
+    // Two slots, by the parity of the call's sequence number: a combine that overlaps the tail of its dispatch can post for
+    // call n+1 while a slower rank has not yet read the word of call n (never further ahead: call n+2 needs that rank's word
+    // of call n+1).
+    uint64_t ll_pull_src[2][kMaxRanks];
     // expert-major dispatch (fused MoE layer): row r = what rank r tells me
     uint64_t em_seq[kMaxRanks];
     // two parities (call sequence odd / even): a fast rank may start its next exchange while a slow one still reads this one

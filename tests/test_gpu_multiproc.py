@@ -230,6 +230,32 @@ def _worker_pressure(rank, world, port, q):
                     want = x.float() * w.masked_fill(idx == -1, 0).sum(dim=1, keepdim=True)
                     assert oracle.calc_diff(want, o.float()) < 9e-4
                 assert sig == first, f"seed {seed} repeat {rep}: results differ from the first repeat"
+        # Pairs issued back to back with no host synchronisation and nothing between the two kernels: the combine then overlaps
+        # the tail of its dispatch, and a fast rank can announce the next call's source before a slow rank has read this call's.
+        # The zero-copy buffers of the two parities hold DIFFERENT expert outputs, so picking up the wrong announcement (or a
+        # stale row number) changes the result.
+        x = make_tokens(T, H, "cuda", seed=7 + rank)
+        idx, w = make_routing(T, E, K, "cuda", seed=7 + rank, masked_fraction=0.02)
+        want = {}
+        for par in range(2):
+            (px, ps), cnt, h, _, _ = buf.low_latency_dispatch(x, idx, T, E, use_fp8=True)
+            y = (oracle.per_token_cast_back(px.view(-1, H), ps.view(-1, H // 128)).view(px.shape) * (1.0 + par)).to(torch.bfloat16)
+            buf.get_next_low_latency_combine_buffer(h).copy_(y)
+            o, _, _ = buf.low_latency_combine(y, idx, w, h, zero_copy=True)
+            torch.cuda.synchronize()
+            dist.barrier()
+            want[par] = o.clone()
+        assert not torch.equal(want[0], want[1])
+        outs = [torch.empty(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(60)]
+        for it in range(60):
+            if rank == world - 1 and it % 7 == 3:
+                torch.cuda._sleep(300000)  # the last rank falls behind now and then
+            _, _, h, _, _ = buf.low_latency_dispatch(x, idx, T, E, use_fp8=True)
+            buf.low_latency_combine(y, idx, w, h, zero_copy=True, out=outs[it])
+        torch.cuda.synchronize()
+        buf.check_status()
+        for it in range(60):
+            assert torch.equal(outs[it], want[it % 2]), f"back-to-back pair {it} differs"
         buf.destroy()
         dist.destroy_process_group()
         q.put((rank, "ok"))

@@ -414,10 +414,11 @@ __global__ void __launch_bounds__(kStageReduceThreads) stage_reduce_kernel(const
         for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
-        for (int k0 = 0; k0 < num_topk; k0 += 4) {
-            int4 v[4][U];
+        // eight selections x two columns: sixteen 16-byte loads in flight per lane before the first one is consumed
+        for (int k0 = 0; k0 < num_topk; k0 += 8) {
+            int4 v[8][U];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < 8; ++kk) {
                 const int k = k0 + kk;
                 const bool kv = k < num_topk && ((valid >> k) & 1u);
 #pragma unroll
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(kStageReduceThreads) stage_reduce_kernel(const
                 }
             }
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < 8; ++kk) {
                 const float wk = __shfl_sync(0xffffffffu, my_w, (k0 + kk) & 31);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {

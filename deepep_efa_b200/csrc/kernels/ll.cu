@@ -601,8 +601,8 @@ __global__ void __launch_bounds__(kLLThreads, 1) combine(const __grid_constant__
 }
 
 // Pull form: the expert outputs of every rank sit in its symmetric buffer, so the home rank reads the K rows of a token
-// where dispatch put them (send_row) and reduces them in registers. The only signalling is one mailbox word per
-// (expert rank, home rank): "outputs final, at this offset".
+// where dispatch put them (send_row) and reduces them in registers. The only signalling is one self-validating word per
+// (expert rank, home rank): "outputs final, at this offset" (ControlBlock::ll_pull_src).
 template <int V>
 __global__ void __launch_bounds__(kLLThreads, 1) combine_pull(const __grid_constant__ ArgPack<LLCombineArgs, V> pack) {
     pdl_release_successor();

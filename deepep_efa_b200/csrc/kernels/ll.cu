@@ -1,7 +1,8 @@
 // Low-latency dispatch / combine for ~128 tokens per rank over one NVSwitch domain.
 //
 // dispatch (one launch):
-//   * every rank all-gathers its per-expert selection counts (E ints per peer, one release flag),
+//   * every rank all-gathers its per-expert selection counts (E words per peer; every word carries a validity tag of the
+//     call, so there is no flag and no release behind them, and a receiver polls exactly the words it uses),
 //   * one CTA per token quantises the row in registers (BF16 -> e4m3, one scale per 128 channels) while
 //     the counts are in flight, then stores it K times straight into the FINAL position of the peers'
 //     packed_recv_x: row `sum_{src<me} count[src][e] + slot` of expert e, which every sender can compute
@@ -13,7 +14,8 @@
 //   * pull (outputs in symmetric memory: the zero-copy buffer or an arena tensor): every rank posts "my outputs are
 //     final, at this offset" to all home ranks; one CTA per token then loads the token's K rows straight from the
 //     peers (their position was recorded by dispatch), does sum_k w[t,k] * row in fp32 registers and writes BF16 once.
-//     No stage buffer, no second pass, one flag hop;
+//     No stage buffer, no second pass, one self-validating word per peer. When it directly follows the dispatch of its
+//     handle it overlaps that kernel's wait for the last rows (see combine_pull);
 //   * push (outputs in ordinary device memory): expert ranks push their BF16 rows into the home rank's
 //     [E][max_tokens] stage (address = (expert, token), so no metadata travels), the home rank waits per source,
 //     then reduces as above.

@@ -271,6 +271,8 @@ class Buffer:
         zero-copy; anything else is staged through one local copy first."""
         if self._hier is not None:
             return self._hier.node_buf.empty_symmetric(shape, dtype)
+        if self._cpu is not None or self.runtime is None:
+            return torch.empty(list(shape), dtype=dtype)  # CPU backend: there is no peer-mapped memory, an ordinary tensor serves
         return self.runtime.alloc_symmetric(list(shape), dtype)
 
     @staticmethod

@@ -65,6 +65,13 @@ def _worker(rank, world, port, q):
         sim = oracle.per_token_cast_back(px.view(-1, H), ps.view(-1, H // 128)).view(px.shape)
         out, _, _ = buf.low_latency_combine(sim, topk_idx, topk_w, ll_handle)
         assert oracle.calc_diff(ref, out.float()) < 9e-4
+        # a program written for the GPU path keeps its expert outputs in Buffer.empty_symmetric: on the CPU backend that is an
+        # ordinary tensor and the call gives the same result
+        sym = buf.empty_symmetric(list(sim.shape), sim.dtype)
+        sym.copy_(sim)
+        (_, _), _, ll_handle2, _, _ = buf.low_latency_dispatch(x, topk_idx, T, E, use_fp8=True)
+        out2, _, _ = buf.low_latency_combine(sym, topk_idx, topk_w, ll_handle2)
+        assert torch.equal(out2, out)
         buf.destroy()
         dist.destroy_process_group()
         q.put((rank, "ok"))
